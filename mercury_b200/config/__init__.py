@@ -8,6 +8,7 @@ from .engine_config import (  # noqa: F401
 from .model_config import (  # noqa: F401
     Architecture,
     ConfigError,
+    FegenexConfig,
     ModelConfig,
     Qwen2Config,
     architecture_named,

@@ -146,6 +146,97 @@ class Qwen2Config(ModelConfig):
         return out
 
 
+# --------------------------------------------------------------------------- Fegenex
+
+_FEGENEX_MIXER_KEYS = {
+    "attention": ("heads", "kv_heads", "dim", "vdim", "scale"),
+    "mingru": ("width",),
+    "rglru": ("width", "blocks", "conv"),
+}
+
+
+@dataclass(frozen=True)
+class FegenexConfig(ModelConfig):
+    """A Fegenex decoder: a list of layers, each with one of three mixers (attention whose
+    heads' weights are mixed, a minGRU, a real-gated linear recurrent unit behind a short
+    convolution) and an optional gated feed-forward. config.json keys: `architecture`,
+    `width`, `vocab`, `max_positions`, `norm.eps`, and `layers`, a list of
+    `{"type", "mixer": {...}, "mlp": {"kind": "dense", "ff"} | null}`. Every size and
+    constant of a layer is in its own entry, so layers may differ in all of them."""
+
+    width: int
+    vocab: int
+    max_positions: int
+    norm_eps: float
+    layers: tuple = ()
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "FegenexConfig":
+        def need(table: dict, key: str, where: str) -> Any:
+            if key not in table:
+                raise ConfigError(f"config.json has no {key!r} in {where}, which Fegenex needs")
+            return table[key]
+
+        layers = []
+        for index, layer in enumerate(need(raw, "layers", "the model")):
+            where = f"layer {index}"
+            kind = need(layer, "type", where)
+            if kind not in _FEGENEX_MIXER_KEYS:
+                raise ConfigError(f"{where}: mixer type {kind!r} is not one of "
+                                  f"{', '.join(sorted(_FEGENEX_MIXER_KEYS))}")
+            mixer = dict(need(layer, "mixer", where))
+            for key in _FEGENEX_MIXER_KEYS[kind]:
+                need(mixer, key, f"{where}'s mixer")
+            if kind == "attention":
+                heads, kv_heads = int(mixer["heads"]), int(mixer["kv_heads"])
+                if heads <= 0 or kv_heads <= 0 or heads % kv_heads:
+                    raise ConfigError(f"{where}: {heads} query heads do not divide into "
+                                      f"{kv_heads} key/value heads")
+                rot = mixer.get("rot") or {}
+                dims = int(rot.get("dims", 0))
+                if dims % 2 or dims > int(mixer["dim"]):
+                    raise ConfigError(f"{where}: rot.dims={dims} must be even and at most "
+                                      f"dim={mixer['dim']}")
+                if dims and "base" not in rot:
+                    raise ConfigError(f"{where}: rot.dims is set but rot.base is missing")
+            if kind == "rglru":
+                if int(mixer["width"]) % int(mixer["blocks"]):
+                    raise ConfigError(f"{where}: width {mixer['width']} does not divide into "
+                                      f"{mixer['blocks']} blocks")
+                if int(mixer["conv"]) < 1:
+                    raise ConfigError(f"{where}: conv={mixer['conv']} taps")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                mlp = dict(mlp)
+                if mlp.get("kind", "dense") != "dense":
+                    raise ConfigError(f"{where}: feed-forward kind {mlp.get('kind')!r} is not built")
+                need(mlp, "ff", f"{where}'s mlp")
+            layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+        if not layers:
+            raise ConfigError("config.json lists no layers")
+        norm = need(raw, "norm", "the model")
+        return cls(
+            architecture=str(raw.get("architecture") or (raw.get("architectures") or ["Fegenex"])[0]),
+            width=int(need(raw, "width", "the model")),
+            vocab=int(need(raw, "vocab", "the model")),
+            max_positions=int(need(raw, "max_positions", "the model")),
+            norm_eps=float(need(norm, "eps", "norm")),
+            layers=tuple(layers),
+        )
+
+    def to_dict(self) -> dict:
+        return {
+            "architecture": self.architecture,
+            "width": self.width,
+            "vocab": self.vocab,
+            "max_positions": self.max_positions,
+            "norm": {"eps": self.norm_eps},
+            "layers": [{"type": l["type"], "mixer": dict(l["mixer"]),
+                        "mlp": dict(l["mlp"]) if l["mlp"] is not None else None}
+                       for l in self.layers],
+        }
+
+
 # --------------------------------------------------------------------------- the registry
 
 @dataclass(frozen=True)
@@ -199,8 +290,17 @@ def read_model_config(folder: str | Path) -> tuple[Architecture, ModelConfig]:
     return config_from_dict(raw)
 
 
+def architecture_name(raw: dict) -> str:
+    """The name a config.json registers under: the first of `architectures`, else the
+    single `architecture`, else Qwen2 (the reference's default, mercury/config.py:46)."""
+    listed = raw.get("architectures")
+    if listed:
+        return str(listed[0])
+    return str(raw.get("architecture") or "Qwen2ForCausalLM")
+
+
 def config_from_dict(raw: dict) -> tuple[Architecture, ModelConfig]:
-    name = (raw.get("architectures") or ["Qwen2ForCausalLM"])[0]
+    name = architecture_name(raw)
     entry = architecture_named(name)
     return entry, entry.config_class.from_dict(raw)
 

@@ -64,6 +64,9 @@ class StepContext:
         self.dtype = dtype
         self.batch: StepBatch | None = None
         self.prenormed = None      # (norm part, its output) left by the product before it
+        # what one layer leaves for a later layer of the same pass (the values of a step's
+        # tokens, say), by a key the model's description chose; emptied before every pass
+        self.carry: dict = {}
 
     def buffer(self, name: str, rows: int, cols: int, dtype=None) -> torch.Tensor:
         return self.workspace.get(name, rows, cols, dtype)
@@ -124,10 +127,17 @@ class ModelRunner:
         self.kv_layers: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
         for cache_id, layer in self.model.cache_layers.items():
             pages = self.cache.pools[layer.group].num_pages
-            store = torch.zeros(
-                (2, pages, layer.need.num_kv_heads, page_size, layer.need.head_dim),
-                dtype=dtype, device=self.device)
-            self.kv_layers[cache_id] = (store[0], store[1])
+            need = layer.need
+            if need.value_head_dim == need.head_dim:
+                store = torch.zeros((2, pages, need.num_kv_heads, page_size, need.head_dim),
+                                    dtype=dtype, device=self.device)
+                self.kv_layers[cache_id] = (store[0], store[1])
+            else:
+                # value heads of another size than the key heads: a tensor each
+                self.kv_layers[cache_id] = tuple(
+                    torch.zeros((pages, need.num_kv_heads, page_size, size), dtype=dtype,
+                                device=self.device)
+                    for size in (need.head_dim, need.value_head_dim))
         self.states: dict[tuple[int, int], torch.Tensor] = {
             key: torch.zeros((max_seqs, *need.shape), dtype=need.dtype, device=self.device)
             for key, need in self.model.state_needs.items()
@@ -176,7 +186,7 @@ class ModelRunner:
         """Bytes of keys and values one token occupies over all cache layers
         (mercury/config.py:73-81)."""
         elem = torch.finfo(self.dtype).bits // 8
-        return sum(2 * l.need.num_kv_heads * l.need.head_dim * elem
+        return sum(l.need.num_kv_heads * (l.need.head_dim + l.need.value_head_dim) * elem
                    for l in self.model.cache_layers.values())
 
     # ------------------------------------------------------------------ sequences
@@ -241,6 +251,8 @@ class ModelRunner:
     def run(self, batch: StepBatch) -> torch.Tensor | None:
         """The model pass over a prepared batch; float32 logits `[wanted, vocab]` or None."""
         self.ctx.batch = batch
+        self.ctx.carry.clear()
+        self.ctx.prenormed = None
         pin = getattr(self.ops, "pin_stream", None)
         if pin is None:
             return self.model.forward(self.ctx, self.kv_layers, self.states)
@@ -416,4 +428,5 @@ def kv_bytes_per_token_of(folder, dtype: torch.dtype) -> int:
     entry, config = read_model_config(folder)
     model = Model(entry.describe(config))
     elem = torch.finfo(dtype).bits // 8
-    return sum(2 * l.need.num_kv_heads * l.need.head_dim * elem for l in model.cache_layers.values())
+    return sum(l.need.num_kv_heads * (l.need.head_dim + l.need.value_head_dim) * elem
+               for l in model.cache_layers.values())

@@ -24,4 +24,4 @@ from .base import (  # noqa: F401
     register_norm,
     register_position_encoding,
 )
-from . import attention, block, embedding, feedforward, norm, rotary  # noqa: F401,E402
+from . import attention, block, embedding, feedforward, norm, recurrent, rotary  # noqa: F401,E402

@@ -128,3 +128,116 @@ class GroupedQueryAttention(Mixer):
 
 
 register_mixer("grouped_query_attention", GroupedQueryAttention)
+
+
+class MixedHeadAttention(Mixer):
+    """Grouped-query attention whose heads exchange their softmax weights, with key and
+    value heads of different sizes and an optional blend of the values across layers.
+
+    Per token: q, k, v projections with biases; the position encoding on q and k; the value
+    blend; keys and blended values stored in the pages; w_g = softmax(q_g . k * scale) over
+    the keys j <= p (and inside `window`, if one is given); when `head_mix` is set the
+    weights are mixed before they meet the values, w'_h = sum_g M[h, g] w_g with M a learned
+    [heads, heads] matrix, and head h applies w'_h to the values of its own key/value head;
+    an output projection with bias.
+
+    `value_blend` = ("source", key): this layer's values of the step's tokens are left in
+    `ctx.carry[key]` for later layers. ("blend", key): v <- (1 - c) v + c carry[key], with c
+    one learned number (`names["blend"]`); the blended values are what the pages hold.
+
+    `names` maps q, k, v, o (biases: the name + ".b" unless `bias_suffix` says otherwise),
+    mix and blend to checkpoint names behind `prefix`.
+    """
+
+    capturable = True
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 value_dim: int, scale: float, prefix: str, names: dict | None = None,
+                 bias_suffix: str = ".b", head_mix: bool = True,
+                 value_blend: tuple | None = None, window: int = 0,
+                 position_encoding: PartSpec | None = None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads do not divide into {num_kv_heads} groups")
+        self.hidden_size = hidden_size
+        self.num_heads, self.num_kv_heads = num_heads, num_kv_heads
+        self.head_dim, self.value_dim = head_dim, value_dim
+        self.scale = float(scale)
+        self.prefix = prefix
+        self.names = {"q": "q", "k": "k", "v": "v", "o": "o", "mix": "talk", "blend": "vmix"}
+        self.names.update(names or {})
+        self.bias_suffix = bias_suffix
+        self.head_mix = bool(head_mix)
+        self.value_blend = tuple(value_blend) if value_blend else None
+        if self.value_blend and self.value_blend[0] not in ("source", "blend"):
+            raise ValueError(f"value_blend role {self.value_blend[0]!r}")
+        self.window = int(window)
+        self.position = build_part("position_encoding", position_encoding or PartSpec("none", {}))
+        if self.position.fused_form() is None:
+            raise ValueError("this mixer takes a rotary encoding or none")
+        self.q_size = num_heads * head_dim
+        self.k_size = num_kv_heads * head_dim
+        self.v_size = num_kv_heads * value_dim
+        self.qkv_weight = self.qkv_b = self.out_weight = self.out_b = None
+        self.mix = self.blend = None
+
+    def cache_need(self):
+        return CacheNeed(self.num_kv_heads, self.head_dim, self.window, self.value_dim)
+
+    def tensor_specs(self):
+        p, h, n, b = self.prefix, self.hidden_size, self.names, self.bias_suffix
+        specs = [TensorSpec(p + n["q"], (self.q_size, h)), TensorSpec(p + n["q"] + b, (self.q_size,)),
+                 TensorSpec(p + n["k"], (self.k_size, h)), TensorSpec(p + n["k"] + b, (self.k_size,)),
+                 TensorSpec(p + n["v"], (self.v_size, h)), TensorSpec(p + n["v"] + b, (self.v_size,)),
+                 TensorSpec(p + n["o"], (h, self.num_heads * self.value_dim)),
+                 TensorSpec(p + n["o"] + b, (h,))]
+        if self.head_mix:
+            specs.append(TensorSpec(p + n["mix"], (self.num_heads, self.num_heads),
+                                    init="eye_normal", std=0.1))
+        if self.value_blend and self.value_blend[0] == "blend":
+            specs.append(TensorSpec(p + n["blend"], (), std=0.1, mean=0.4))
+        return specs + self.position.tensor_specs()
+
+    def load(self, tensors, setup):
+        p, n, b = self.prefix, self.names, self.bias_suffix
+
+        def packed(suffix):
+            parts = [setup.place(tensors[p + n[key] + suffix]) for key in ("q", "k", "v")]
+            widest = torch.float32 if any(t.dtype == torch.float32 for t in parts) else parts[0].dtype
+            return torch.cat([t.to(widest) for t in parts], dim=0).contiguous()
+
+        self.qkv_weight, self.qkv_b = packed(""), packed(b)
+        self.out_weight = setup.place(tensors[p + n["o"]])
+        self.out_b = setup.place(tensors[p + n["o"] + b])
+        # the weights of the softmax are float32, and so is what mixes them
+        self.mix = setup.place(tensors[p + n["mix"]]).float().contiguous() if self.head_mix else None
+        if self.value_blend and self.value_blend[0] == "blend":
+            self.blend = setup.place(tensors[p + n["blend"]]).float().reshape(1).contiguous()
+        self.position.load(tensors, setup)
+
+    def forward(self, x, ctx, cache, state):
+        tokens = x.shape[0]
+        ops = ctx.ops
+        qkv = ctx.buffer("qkv_split", tokens, self.q_size + self.k_size + self.v_size)
+        ops.linear(x, self.qkv_weight, self.qkv_b, qkv)
+        tables = self.position.rotary_tables() if self.position.fused_form() == "rotary" else None
+        keep = blend_from = None
+        if self.value_blend:
+            role, key = self.value_blend
+            if role == "source":
+                keep = ctx.carry[key] = ctx.buffer("values_" + str(key), tokens, self.v_size)
+            else:
+                blend_from = ctx.carry.get(key)
+                if blend_from is None or blend_from.shape[1] != self.v_size:
+                    raise ValueError(f"{self.prefix}: no layer before this one left values of "
+                                     f"width {self.v_size} under {key!r}")
+        layout = (self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim)
+        ops.rope_blend_store(qkv, layout, tables, ctx.batch, cache, blend_from, self.blend, keep)
+        attended = ctx.buffer("attended_v", tokens, self.num_heads * self.value_dim)
+        ops.mixed_head_attention(qkv, layout, ctx.batch, cache, self.scale, self.window, self.mix,
+                                 attended)
+        out = ctx.buffer("sublayer_out", tokens, self.hidden_size, dtype="float32")
+        ops.linear(attended, self.out_weight, self.out_b, out)
+        return out
+
+
+register_mixer("mixed_head_attention", MixedHeadAttention)

@@ -76,13 +76,15 @@ import torch
 @dataclass(frozen=True)
 class TensorSpec:
     """One checkpoint tensor a part expects. `kind` is "float" or "int"; `init` says how the
-    random-weights mode fills it: "normal" = N(0, std), "ones_normal" = 1 + N(0, std)."""
+    random-weights mode fills it: "normal" = mean + N(0, std), "ones_normal" = 1 + N(0, std),
+    "eye_normal" = identity + N(0, std) (a square matrix that starts near doing nothing)."""
 
     name: str
     shape: tuple[int, ...]
     kind: str = "float"
     init: str = "normal"
     std: float = 0.02
+    mean: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -96,11 +98,17 @@ class PartSpec:
 @dataclass(frozen=True)
 class CacheNeed:
     """Keys and values a mixer keeps per token. `window` = 0 keeps every key; a positive
-    window keeps the last `window` (pages behind it are given back)."""
+    window keeps the last `window` (pages behind it are given back). `value_dim` is the
+    size of a value head where it differs from the key head's (0: the same)."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: int = 0
+
+    @property
+    def value_head_dim(self) -> int:
+        return self.value_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -155,8 +163,8 @@ class PartSetup:
 
 @dataclass
 class LayerCache:
-    """One cache layer as a mixer sees it: K and V pages `[pages, kv_heads, page_size,
-    head_dim]`, the block table of its group for this step `[sequences, max_pages]` int32
+    """One cache layer as a mixer sees it: K pages `[pages, kv_heads, page_size, head_dim]`
+    and V pages of the same form (with the value head's size), the block table of its group for this step `[sequences, max_pages]` int32
     (-1 where a page was given back), and whether this call stores new keys or only reads
     what another layer stored."""
 

@@ -45,4 +45,50 @@ class PreNormBlock:
         return ff.forward(x, ctx)
 
 
+class SandwichBlock:
+    """A norm before AND behind each sublayer: h <- h + post(mixer(pre(h))), then, where the
+    block has a feed-forward, h <- h + post'(ff(pre'(h))). The sums are made by the norm
+    behind the sublayer (`normed_add`), which also computes the norm that comes next, so
+    the block leaves no pending delta."""
+
+    def __init__(self, mixer: PartSpec, mixer_norm: PartSpec, mixer_post_norm: PartSpec,
+                 feed_forward: PartSpec | None = None, feed_forward_norm: PartSpec | None = None,
+                 feed_forward_post_norm: PartSpec | None = None):
+        self.mixer = build_part("mixer", mixer)
+        self.mixer_norm = build_part("norm", mixer_norm)
+        self.mixer_post_norm = build_part("norm", mixer_post_norm)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = None
+        if feed_forward is not None:
+            if feed_forward_norm is None or feed_forward_post_norm is None:
+                raise ValueError("a feed-forward needs the norms before and behind it")
+            self.feed_forward = build_part("feed_forward", feed_forward)
+            self.feed_forward_norm = build_part("norm", feed_forward_norm)
+            self.feed_forward_post_norm = build_part("norm", feed_forward_post_norm)
+
+    def mixers(self):
+        return [self.mixer]
+
+    def parts(self):
+        out = [self.mixer_norm, self.mixer, self.mixer_post_norm]
+        if self.feed_forward is not None:
+            out += [self.feed_forward_norm, self.feed_forward, self.feed_forward_post_norm]
+        return out
+
+    def first_norm(self):
+        return self.mixer_norm
+
+    def forward(self, h, delta, ctx, caches, states, next_norm=None):
+        x = self.mixer_norm.add_norm(h, delta, ctx)
+        mixed = self.mixer.forward(x, ctx, caches[0], states[0])
+        if self.feed_forward is None:
+            self.mixer_post_norm.normed_add(h, mixed, ctx, then_norm=next_norm)
+            return None
+        self.mixer_post_norm.normed_add(h, mixed, ctx, then_norm=self.feed_forward_norm)
+        x = self.feed_forward_norm.add_norm(h, None, ctx)
+        self.feed_forward_post_norm.normed_add(h, self.feed_forward.forward(x, ctx), ctx,
+                                               then_norm=next_norm)
+        return None
+
+
 register_arrangement("pre_norm", PreNormBlock)
+register_arrangement("sandwich_norm", SandwichBlock)

@@ -37,6 +37,32 @@ class TokenEmbedding(Embedding):
         return h
 
 
+class PositionedEmbedding(TokenEmbedding):
+    """Token row plus a learned vector per position (position counted from 0 in each
+    sequence), neither scaled: stream[t] = table[token[t]] + positions[position[t]]."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str, position_name: str,
+                 max_positions: int):
+        super().__init__(vocab_size, hidden_size, weight_name)
+        self.position_name = position_name
+        self.max_positions = max_positions
+        self.position_table = None
+
+    def tensor_specs(self):
+        return super().tensor_specs() + [
+            TensorSpec(self.position_name, (self.max_positions, self.hidden_size))]
+
+    def load(self, tensors, setup):
+        super().load(tensors, setup)
+        self.position_table = setup.place_named(tensors, self.position_name)
+
+    def forward(self, token_ids, ctx):
+        h = ctx.buffer("residual", token_ids.shape[0], self.hidden_size, dtype="float32")
+        ctx.ops.embed(token_ids, self.table, h, positions=ctx.batch.positions,
+                      position_table=self.position_table)
+        return h
+
+
 class LinearHead(Head):
     capturable = True
 
@@ -59,4 +85,5 @@ class LinearHead(Head):
 
 
 register_embedding("lookup", TokenEmbedding)
+register_embedding("lookup_learned_positions", PositionedEmbedding)
 register_head("linear", LinearHead)

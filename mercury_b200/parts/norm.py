@@ -11,6 +11,9 @@ from __future__ import annotations
 
 from .base import Norm, TensorSpec, register_norm
 
+# A norm may also stand BEHIND a sublayer (`RMSNorm.normed_add`): the sublayer's output is
+# normalised and only then added to the stream.
+
 
 class PendingNorm:
     """A norm that has not run yet: the float32 stream, the weight and eps (and optionally
@@ -43,21 +46,54 @@ class PendingScaled(PendingNorm):
         self.x, self.ss_part = x, ss_part
 
 
+class Computed:
+    """A norm's output that a fused kernel has already written; `materialize()` hands it over."""
+
+    def __init__(self, out):
+        self.out = out
+        self.shape, self.dtype = out.shape, out.dtype
+
+    def materialize(self):
+        return self.out
+
+
 class RMSNorm(Norm):
     capturable = True
 
-    def __init__(self, size: int, eps: float, weight_name: str, init_std: float = 0.05):
+    def __init__(self, size: int, eps: float, weight_name: str, init_std: float = 0.05,
+                 gain: str = "vector"):
+        """`gain` "vector": one learned number per feature; "scalar": the checkpoint holds a
+        single number for all features (it is spread over a vector when loaded, so the
+        kernels are the same)."""
+        if gain not in ("vector", "scalar"):
+            raise ValueError(f"gain={gain!r} is neither 'vector' nor 'scalar'")
         self.size = size
         self.eps = eps
         self.weight_name = weight_name
         self.init_std = init_std
+        self.gain = gain
         self.weight = None
 
     def tensor_specs(self):
-        return [TensorSpec(self.weight_name, (self.size,), init="ones_normal", std=self.init_std)]
+        shape = (self.size,) if self.gain == "vector" else ()
+        return [TensorSpec(self.weight_name, shape, init="ones_normal", std=self.init_std)]
 
     def load(self, tensors, setup):
-        self.weight = setup.place(tensors[self.weight_name])
+        weight = setup.place(tensors[self.weight_name])
+        if self.gain == "scalar":
+            weight = weight.reshape(1).expand(self.size).contiguous()
+        self.weight = weight
+
+    def normed_add(self, h, delta, ctx, then_norm=None):
+        """h <- h + norm(delta): this norm applied to a sublayer's OUTPUT before it joins the
+        float32 stream. With `then_norm` (an RMSNorm over the same width) the same kernel
+        also leaves that norm's output of the new stream in `ctx.prenormed`."""
+        follow = then_norm if (isinstance(then_norm, RMSNorm) and then_norm.size == self.size) else None
+        out = ctx.buffer("normed", h.shape[0], self.size) if follow is not None else None
+        ctx.ops.rmsnorm_add(h, delta, self.weight, self.eps,
+                            follow.weight if follow is not None else None,
+                            follow.eps if follow is not None else 0.0, out)
+        ctx.prenormed = (follow, Computed(out)) if follow is not None else None
 
     def add_norm(self, h, delta, ctx, rows=None, defer=False):
         """`defer=True` says that the consumer takes a `PendingNorm`; one is returned when
@@ -78,3 +114,4 @@ class RMSNorm(Norm):
 
 
 register_norm("rmsnorm", RMSNorm)
+register_norm("rmsnorm_scalar", lambda **params: RMSNorm(gain="scalar", **params))

@@ -17,7 +17,11 @@ from .base import PositionEncoding, register_position_encoding
 class RotaryEncoding(PositionEncoding):
     capturable = True
 
-    def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None):
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None,
+                 table_precision: str = "float32"):
+        """`table_precision` "float64": angles, cosines and sines are computed in 64-bit and
+        rounded once to the float32 tables."""
+        self.table_precision = table_precision
         self.head_dim = head_dim
         self.theta = float(theta)
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
@@ -28,16 +32,18 @@ class RotaryEncoding(PositionEncoding):
 
     def load(self, tensors, setup):
         def tables():
-            exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
+            real = torch.float64 if self.table_precision == "float64" else torch.float32
+            exponent = torch.arange(0, self.rotary_dim, 2, dtype=real) / self.rotary_dim
             inv_freq = 1.0 / (self.theta ** exponent)
-            positions = torch.arange(setup.max_positions, dtype=torch.float32)
+            positions = torch.arange(setup.max_positions, dtype=real)
             angles = torch.outer(positions, inv_freq)
-            return (angles.cos().to(setup.device).contiguous(),
-                    angles.sin().to(setup.device).contiguous())
+            return (angles.cos().float().to(setup.device).contiguous(),
+                    angles.sin().float().to(setup.device).contiguous())
 
         # every layer with the same constants reads the same pair of tables
         self.cos, self.sin = setup.derived(
-            ("rotary", self.rotary_dim, self.theta, setup.max_positions, str(setup.device)), tables)
+            ("rotary", self.rotary_dim, self.theta, setup.max_positions, str(setup.device),
+             self.table_precision), tables)
 
     def fused_form(self):
         return "rotary"

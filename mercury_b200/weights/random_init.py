@@ -37,6 +37,10 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, vocab_limit: 
     values = torch.randn(spec.shape, generator=gen, dtype=torch.float32) * spec.std
     if spec.init == "ones_normal":
         values = values + 1.0
+    elif spec.init == "eye_normal":
+        values = values + torch.eye(spec.shape[-1], dtype=torch.float32).expand(spec.shape)
+    elif spec.mean:
+        values = values + spec.mean
     return values.to(dtype)
 
 
@@ -51,7 +55,7 @@ def random_tensors(config: ModelConfig, seed: int, dtype: torch.dtype = torch.bf
     out = {}
     for spec in model.tensor_specs():
         if std is not None and spec.init == "normal":
-            spec = TensorSpec(spec.name, spec.shape, spec.kind, spec.init, std)
+            spec = TensorSpec(spec.name, spec.shape, spec.kind, spec.init, std, spec.mean)
         out[spec.name] = random_tensor(spec, seed, dtype)
     return out
 

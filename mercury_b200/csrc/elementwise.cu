@@ -24,6 +24,84 @@ __global__ void embed_kernel(const int* __restrict__ ids, const void* __restrict
         out[(int64_t)t * hidden + c] = ok ? load_as_float(table, base + c, table_dtype) : 0.f;
 }
 
+// The same with a learned vector per position added: out[t, :] = table[ids[t], :] +
+// pos_table[positions[t], :], neither scaled.
+__global__ void embed_positions_kernel(const int* __restrict__ ids, const void* __restrict__ table,
+                                       int table_dtype, const int* __restrict__ positions,
+                                       const void* __restrict__ pos_table, int pos_dtype,
+                                       int max_positions, float* __restrict__ out, int hidden,
+                                       int vocab) {
+    grid_dependency_sync();
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const int pos = positions[t];
+    const bool ok = id >= 0 && id < vocab && pos >= 0 && pos < max_positions;
+#ifdef MB_BOUNDS_CHECK
+    if (threadIdx.x == 0) {
+        if (id < 0 || id >= vocab) check_report(MB_CHECK_TOKEN, id, vocab);
+        else if (!ok) check_report(MB_CHECK_POSITION, pos, max_positions);
+    }
+#endif
+    const int64_t base = (int64_t)(ok ? id : 0) * hidden;
+    const int64_t pbase = (int64_t)(ok ? pos : 0) * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+        out[(int64_t)t * hidden + c] =
+            ok ? load_as_float(table, base + c, table_dtype) + load_as_float(pos_table, pbase + c, pos_dtype)
+               : 0.f;
+}
+
+// A norm BEHIND a sublayer: h <- h + delta * rsqrt(mean(delta^2) + eps) * w, and, when the
+// norm that follows is given, out = h * rsqrt(mean(h^2) + eps2) * w2 of the new h in the
+// same pass. One block per row, the new row kept in shared memory between the two sums.
+template <typename TD, typename TO>
+__global__ void rmsnorm_add_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                   const void* __restrict__ w, int w_dtype, float eps,
+                                   const void* __restrict__ w2, int w2_dtype, float eps2,
+                                   TO* __restrict__ out, int hidden) {
+    grid_dependency_sync();
+    extern __shared__ float row_s[];
+    __shared__ float scratch[33];
+    const int64_t at = (int64_t)blockIdx.x * hidden;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float d = to_float(delta[at + c]);
+        row_s[c] = d;
+        ss += d * d;
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = rsqrtf(ss / (float)hidden + eps);
+    float ss2 = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float x = h[at + c] + row_s[c] * rstd * load_as_float(w, c, w_dtype);
+        h[at + c] = x;
+        row_s[c] = x;
+        ss2 += x * x;
+    }
+    if (w2 == nullptr) return;
+    ss2 = block_sum(ss2, scratch);
+    const float rstd2 = rsqrtf(ss2 / (float)hidden + eps2);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+        out[at + c] = from_float<TO>(row_s[c] * rstd2 * load_as_float(w2, c, w2_dtype));
+}
+
+// out[t, i] = act(gate_up[t, i]) * gate_up[t, width + i]; act 0: SiLU, 1: the tanh form of
+// GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t total,
+                                 int width, int act) {
+    grid_dependency_sync();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / width;
+        const int c = (int)(i - t * width);
+        const float g = to_float(gate_up[t * 2 * width + c]);
+        const float u = to_float(gate_up[t * 2 * width + width + c]);
+        const float a = act == 0 ? g / (1.f + expf(-g))
+                                 : 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+        out[i] = from_float<T>(a * u);
+    }
+}
+
 // Token ids that were not known on the host when the step was put together (the step was
 // launched while the step before was still running): ids[t] = sampled[from[t]] where
 // from[t] >= 0, taken from the tokens the step before has sampled on the device.
@@ -423,6 +501,66 @@ MB_EXPORT int mb_embed(const int* ids, const void* table, int table_dtype, float
     if (tokens <= 0) return MB_OK;
     MB_LAUNCH((embed_kernel), tokens, 256, 0, (cudaStream_t)stream, ids, table, table_dtype, out, hidden,
                                                             vocab);
+    return launch_status();
+}
+
+MB_EXPORT int mb_embed_positions(const int* ids, const void* table, int table_dtype,
+                                 const int* positions, const void* pos_table, int pos_dtype,
+                                 int max_positions, float* out, int tokens, int hidden, int vocab,
+                                 void* stream) {
+    if (tokens <= 0) return MB_OK;
+    MB_LAUNCH((embed_positions_kernel), tokens, 256, 0, (cudaStream_t)stream, ids, table, table_dtype,
+              positions, pos_table, pos_dtype, max_positions, out, hidden, vocab);
+    return launch_status();
+}
+
+// delta_dtype / out_dtype: MB_F32 or MB_BF16. w2 null: only the sum into h is made.
+MB_EXPORT int mb_rmsnorm_add(float* h, const void* delta, int delta_dtype, const void* w, int w_dtype,
+                             float eps, const void* w2, int w2_dtype, float eps2, void* out,
+                             int out_dtype, int count, int hidden, void* stream) {
+    if (count <= 0) return MB_OK;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 160 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    typedef __nv_bfloat16 bf;
+#define MB_RA_CASE(TD, TO)                                                                        \
+    do {                                                                                          \
+        static size_t raised = 0;                                                                 \
+        if (smem > 48 * 1024 && smem > raised) {                                                  \
+            if (cudaFuncSetAttribute(rmsnorm_add_kernel<TD, TO>,                                  \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=   \
+                cudaSuccess)                                                                      \
+                return MB_ERR_UNSUPPORTED_SIZE;                                                   \
+            raised = smem;                                                                        \
+        }                                                                                         \
+        MB_LAUNCH((rmsnorm_add_kernel<TD, TO>), count, threads, smem, s, h, (const TD*)delta, w,  \
+                  w_dtype, eps, w2, w2_dtype, eps2, (TO*)out, hidden);                            \
+    } while (0)
+    if (delta_dtype == MB_F32 && out_dtype == MB_F32) MB_RA_CASE(float, float);
+    else if (delta_dtype == MB_F32 && out_dtype == MB_BF16) MB_RA_CASE(float, bf);
+    else if (delta_dtype == MB_BF16 && out_dtype == MB_F32) MB_RA_CASE(bf, float);
+    else if (delta_dtype == MB_BF16 && out_dtype == MB_BF16) MB_RA_CASE(bf, bf);
+    else return MB_ERR_BAD_DTYPE;
+#undef MB_RA_CASE
+    return launch_status();
+}
+
+MB_EXPORT int mb_gated_act(const void* gate_up, void* out, int tokens, int width, int dtype, int act,
+                           void* stream) {
+    const int64_t total = (int64_t)tokens * width;
+    if (total <= 0) return MB_OK;
+    if (act != 0 && act != 1) return MB_ERR_UNSUPPORTED_SIZE;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MB_F32)
+        MB_LAUNCH((gated_act_kernel<float>), blocks, 256, 0, s, (const float*)gate_up, (float*)out, total,
+                  width, act);
+    else if (dtype == MB_BF16)
+        MB_LAUNCH((gated_act_kernel<__nv_bfloat16>), blocks, 256, 0, s, (const __nv_bfloat16*)gate_up,
+                  (__nv_bfloat16*)out, total, width, act);
+    else
+        return MB_ERR_BAD_DTYPE;
     return launch_status();
 }
 

@@ -1,0 +1,226 @@
+// Recurrent mixers: a minGRU and a gated linear recurrence behind a short causal
+// convolution. The state of a request lives in float32 in its slot, `state[slot]`, and
+// every kernel here runs a step's tokens of sequence s (rows q_start[s] .. q_start[s+1]-1
+// of the batch) in order from the state the step before left. Gates, decays and the state
+// are float32 in both engines; only the output (the input of the next product) is stored
+// in the activation type. One thread owns one channel, so a channel's arithmetic is the
+// same however the tokens were cut into steps.
+#include "common.cuh"
+
+namespace mb {
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// pre: [tokens][3 * width] float32 = [gate z | candidate u | output gate g] before their
+// activations. S <- (1 - z) S + z c with z = sigmoid(.), c = u + 1/2 (u >= 0) or sigmoid(u);
+// out = S * silu(g).
+template <typename T>
+__global__ void mingru_scan_kernel(const float* __restrict__ pre, float* __restrict__ state,
+                                   const int* __restrict__ q_start, const int* __restrict__ slots,
+                                   T* __restrict__ out, int width) {
+    grid_dependency_sync();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int seq = blockIdx.y;
+    const int begin = q_start[seq], end = q_start[seq + 1];
+    if (c >= width || begin >= end) return;
+    float* cell = state + (int64_t)slots[seq] * width + c;
+    float s = *cell;
+#pragma unroll 4
+    for (int t = begin; t < end; ++t) {
+        const float* row = pre + (int64_t)t * 3 * width;
+        const float z = sigmoid_f(row[c]);
+        const float u = row[width + c];
+        const float g = row[2 * width + c];
+        const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+        s = (1.f - z) * s + z * cand;
+        out[(int64_t)t * width + c] = from_float<T>(s * (g * sigmoid_f(g)));
+    }
+    *cell = s;
+}
+
+// u[t][c] = sum_k taps_w[c][k] * x[t - (taps - 1 - k)][c] + bias[c], x = pre[:, offset + c]
+// (row stride ld). Inputs from before this step come from the state: state[slot][j][c] is
+// the input j tokens before the step's first token (j = 1 .. taps - 1; zero before the
+// sequence began, because a fresh slot is zeroed). The state is not changed here.
+__global__ void causal_conv_kernel(const float* __restrict__ pre, int ld, int offset,
+                                   const float* __restrict__ taps_w, const float* __restrict__ bias,
+                                   const float* __restrict__ state, const int* __restrict__ q_start,
+                                   const int* __restrict__ slots, const int* __restrict__ seq_of_token,
+                                   float* __restrict__ u, int width, int taps) {
+    grid_dependency_sync();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = blockIdx.y;
+    const int seq = seq_of_token[t];
+    if (c >= width || seq < 0) return;
+    const int begin = q_start[seq];
+    const int at = t - begin;
+    const float* past = state + (int64_t)slots[seq] * taps * width;
+    float acc = 0.f;
+    for (int k = 0; k < taps; ++k) {
+        const int src = at - (taps - 1 - k);
+        const float x = src >= 0 ? pre[(int64_t)(begin + src) * ld + offset + c]
+                                 : past[(int64_t)(-src) * width + c];
+        acc = fmaf(taps_w[c * taps + k], x, acc);
+    }
+    u[(int64_t)t * width + c] = acc + bias[c];
+}
+
+// gates[t][kind * width + b * size + o] = sigmoid(sum_i w[kind][b][i][o] * u[t][b * size + i]
+// + bias[kind][b][o]): block-diagonal products in float32, the weights held input-major so
+// that consecutive threads (outputs o) read consecutive addresses. A block computes 128
+// outputs of one (kind, block b) for 16 tokens; i ascends, so the sum's order is fixed.
+constexpr int BG_TOKENS = 16;
+
+__global__ void __launch_bounds__(128)
+block_gates_kernel(const float* __restrict__ u, const float* __restrict__ w,
+                   const float* __restrict__ bias, float* __restrict__ gates, int tokens, int width,
+                   int blocks, int size, int kinds) {
+    grid_dependency_sync();
+    extern __shared__ float u_s[];          // [BG_TOKENS][size]
+    const int per = (size + 127) / 128;     // output tiles per (kind, block)
+    const int otile = blockIdx.x % per;
+    const int b = (blockIdx.x / per) % blocks;
+    const int kind = blockIdx.x / (per * blocks);
+    const int t0 = blockIdx.y * BG_TOKENS;
+    for (int idx = threadIdx.x; idx < BG_TOKENS * size; idx += blockDim.x) {
+        const int tt = idx / size, i = idx - tt * size;
+        u_s[idx] = t0 + tt < tokens ? u[(int64_t)(t0 + tt) * width + b * size + i] : 0.f;
+    }
+    __syncthreads();
+    const int o = otile * 128 + threadIdx.x;
+    if (o >= size) return;
+    const float* wp = w + ((int64_t)(kind * blocks + b) * size) * size + o;
+    float acc[BG_TOKENS];
+#pragma unroll
+    for (int tt = 0; tt < BG_TOKENS; ++tt) acc[tt] = 0.f;
+    for (int i = 0; i < size; ++i) {
+        const float wv = wp[(int64_t)i * size];
+#pragma unroll
+        for (int tt = 0; tt < BG_TOKENS; ++tt) acc[tt] = fmaf(wv, u_s[tt * size + i], acc[tt]);
+    }
+    const float bv = bias[(kind * blocks + b) * size + o];
+#pragma unroll
+    for (int tt = 0; tt < BG_TOKENS; ++tt)
+        if (t0 + tt < tokens)
+            gates[(int64_t)(t0 + tt) * kinds * width + kind * width + b * size + o] =
+                sigmoid_f(acc[tt] + bv);
+}
+
+// pre: [tokens][2 * width] float32 = [branch y | convolution input x]; u: the convolution's
+// output; gates: [tokens][2 * width] = [r | i] after their sigmoids.
+// a = exp(-decay_scale * r * softplus_lam), S <- a S + sqrt(1 - a^2) * i * u, out = S * gelu(y).
+// state[slot]: row 0 = S, row j = the convolution's input j tokens back; the rows 1.. are
+// brought up to the end of this step here, after every token's convolution has been taken.
+template <typename T>
+__global__ void gated_recurrence_scan_kernel(const float* __restrict__ pre, const float* __restrict__ u,
+                                             const float* __restrict__ gates,
+                                             const float* __restrict__ softplus_lam, float decay_scale,
+                                             float* __restrict__ state, const int* __restrict__ q_start,
+                                             const int* __restrict__ slots, T* __restrict__ out,
+                                             int width, int taps) {
+    grid_dependency_sync();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int seq = blockIdx.y;
+    const int begin = q_start[seq], end = q_start[seq + 1];
+    if (c >= width || begin >= end) return;
+    float* mine = state + (int64_t)slots[seq] * taps * width + c;
+    const float sp = softplus_lam[c];
+    float s = mine[0];
+#pragma unroll 4
+    for (int t = begin; t < end; ++t) {
+        const float r = gates[(int64_t)t * 2 * width + c];
+        const float i = gates[(int64_t)t * 2 * width + width + c];
+        const float x = u[(int64_t)t * width + c];
+        const float y = pre[(int64_t)t * 2 * width + c];
+        const float a = expf(-decay_scale * r * sp);
+        s = a * s + sqrtf(1.f - a * a) * i * x;
+        out[(int64_t)t * width + c] = from_float<T>(s * gelu_tanh_f(y));
+    }
+    mine[0] = s;
+    const int n = end - begin;
+    float old[16];
+    for (int j = 1; j < taps; ++j) old[j] = mine[(int64_t)j * width];
+    for (int j = 1; j < taps; ++j) {
+        const int idx = n - j;
+        mine[(int64_t)j * width] =
+            idx >= 0 ? pre[(int64_t)(begin + idx) * 2 * width + width + c] : old[j - n];
+    }
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+MB_EXPORT int mb_mingru_scan(const float* pre, float* state, const int* q_start, const int* slots,
+                             void* out, int num_seqs, int width, int dtype, void* stream) {
+    if (num_seqs <= 0 || width <= 0) return MB_OK;
+    if (num_seqs > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    dim3 grid((width + 127) / 128, num_seqs);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MB_F32)
+        MB_LAUNCH((mingru_scan_kernel<float>), grid, 128, 0, s, pre, state, q_start, slots, (float*)out, width);
+    else if (dtype == MB_BF16)
+        MB_LAUNCH((mingru_scan_kernel<__nv_bfloat16>), grid, 128, 0, s, pre, state, q_start, slots,
+                  (__nv_bfloat16*)out, width);
+    else
+        return MB_ERR_BAD_DTYPE;
+    return launch_status();
+}
+
+MB_EXPORT int mb_causal_conv(const float* pre, int ld, int offset, const float* taps_w,
+                             const float* bias, const float* state, const int* q_start,
+                             const int* slots, const int* seq_of_token, float* u, int tokens,
+                             int width, int taps, void* stream) {
+    if (tokens <= 0 || width <= 0) return MB_OK;
+    if (taps < 1 || taps > 16 || tokens > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    dim3 grid((width + 127) / 128, tokens);
+    MB_LAUNCH((causal_conv_kernel), grid, 128, 0, (cudaStream_t)stream, pre, ld, offset, taps_w, bias,
+              state, q_start, slots, seq_of_token, u, width, taps);
+    return launch_status();
+}
+
+// w: [kinds][blocks][size (in)][size (out)] float32; bias: [kinds][blocks][size].
+MB_EXPORT int mb_block_gates(const float* u, const float* w, const float* bias, float* gates,
+                             int tokens, int width, int blocks, int kinds, void* stream) {
+    if (tokens <= 0 || width <= 0) return MB_OK;
+    if (blocks <= 0 || width % blocks) return MB_ERR_UNSUPPORTED_SIZE;
+    const int size = width / blocks;
+    const size_t smem = (size_t)BG_TOKENS * size * sizeof(float);
+    if (smem > 200 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
+    static size_t raised = 0;
+    if (smem > 48 * 1024 && smem > raised) {
+        if (cudaFuncSetAttribute(block_gates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return MB_ERR_UNSUPPORTED_SIZE;
+        raised = smem;
+    }
+    const int rows = (tokens + BG_TOKENS - 1) / BG_TOKENS;
+    if (rows > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    dim3 grid(((size + 127) / 128) * blocks * kinds, rows);
+    MB_LAUNCH((block_gates_kernel), grid, 128, smem, (cudaStream_t)stream, u, w, bias, gates, tokens,
+              width, blocks, size, kinds);
+    return launch_status();
+}
+
+MB_EXPORT int mb_gated_recurrence_scan(const float* pre, const float* u, const float* gates,
+                                       const float* softplus_lam, float decay_scale, float* state,
+                                       const int* q_start, const int* slots, void* out,
+                                       int num_seqs, int width, int taps, int dtype, void* stream) {
+    if (num_seqs <= 0 || width <= 0) return MB_OK;
+    if (taps < 1 || taps > 16 || num_seqs > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    dim3 grid((width + 127) / 128, num_seqs);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MB_F32)
+        MB_LAUNCH((gated_recurrence_scan_kernel<float>), grid, 128, 0, s, pre, u, gates, softplus_lam,
+                  decay_scale, state, q_start, slots, (float*)out, width, taps);
+    else if (dtype == MB_BF16)
+        MB_LAUNCH((gated_recurrence_scan_kernel<__nv_bfloat16>), grid, 128, 0, s, pre, u, gates,
+                  softplus_lam, decay_scale, state, q_start, slots, (__nv_bfloat16*)out, width, taps);
+    else
+        return MB_ERR_BAD_DTYPE;
+    return launch_status();
+}

@@ -292,6 +292,18 @@ class ModelRunner:
         kv_heads = max((l.need.num_kv_heads for l in self.model.cache_layers.values()), default=1)
         return choose(bucket, kv_heads)
 
+    def _warm_up(self, batch: StepBatch) -> None:
+        """One pass outside the capture, so that buffers exist and kernels are loaded. The
+        pass is real: it stores the step's keys (which the replay stores again, the same)
+        and it moves the per-request states on, which the replay must not do a second
+        time; so the states are put back to what they were."""
+        saved = {key: state.clone() for key, state in self.states.items()}
+        self.run(batch)
+        torch.cuda.synchronize(self.device)
+        for key, state in self.states.items():
+            state.copy_(saved[key])
+        torch.cuda.synchronize(self.device)
+
     def _decode_with_graph(self, entries: list[StepEntry], sampled=None) -> torch.Tensor | None:
         """Decode-only steps (one token per entry) replay a CUDA graph captured once per
         batch-size bucket: the launch sequence is fixed and everything that varies (tokens,
@@ -306,8 +318,7 @@ class ModelRunner:
         batch.attention_splits = self._graph_splits(bucket)
         held = self._graphs.get(bucket)
         if held is None:
-            self.run(batch)                       # warm-up: allocates buffers, loads kernels
-            torch.cuda.synchronize(self.device)
+            self._warm_up(batch)
             graph = torch.cuda.CUDAGraph()
             before = self.launch_count(replayed=False)
             # Inside a captured decode step every kernel may be scheduled while the one in
@@ -359,8 +370,7 @@ class ModelRunner:
         if held is None:
             if len(self._shape_graphs) >= self.max_shape_graphs:
                 self._shape_graphs.pop(next(iter(self._shape_graphs)))
-            self.run(batch)                       # warm-up outside the capture
-            torch.cuda.synchronize(self.device)
+            self._warm_up(batch)
             graph = torch.cuda.CUDAGraph()
             before = self.launch_count(replayed=False)
             with torch.cuda.graph(graph):

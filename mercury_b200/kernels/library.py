@@ -75,6 +75,23 @@ _SIGNATURES = {
                                           c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "mb_gemm_skinny_set_slices": [c_int, c_int],
     "mb_patch_tokens": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "mb_embed_positions": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                           c_int, c_int, c_int, c_void_p],
+    "mb_rmsnorm_add": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_float,
+                       c_void_p, c_int, c_int, c_int, c_void_p],
+    "mb_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_mixed_head_attention": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                c_int, c_int, c_float, c_int, c_int, c_void_p],
+    "mb_rope_blend_store": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                            c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_mingru_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "mb_causal_conv": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "mb_block_gates": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_gated_recurrence_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "mb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }

@@ -246,11 +246,31 @@ class CudaOps:
     # ------------------------------------------------------------------ kernels
 
     @_timed("embedding")
-    def embed(self, token_ids, table, out):
+    def embed(self, token_ids, table, out, positions=None, position_table=None):
+        """out = table[token_ids] (+ position_table[positions]) in the float32 stream."""
         self._rows(out)
-        check(self.lib.mb_embed(_ptr(token_ids), _ptr(table), _flag(table.dtype), _ptr(out),
-                                out.shape[0], out.shape[1], table.shape[0], self._stream()),
-              "embed")
+        if position_table is None:
+            check(self.lib.mb_embed(_ptr(token_ids), _ptr(table), _flag(table.dtype), _ptr(out),
+                                    out.shape[0], out.shape[1], table.shape[0], self._stream()),
+                  "embed")
+        else:
+            check(self.lib.mb_embed_positions(
+                _ptr(token_ids), _ptr(table), _flag(table.dtype), _ptr(positions),
+                _ptr(position_table), _flag(position_table.dtype), position_table.shape[0],
+                _ptr(out), out.shape[0], out.shape[1], table.shape[0], self._stream()), "embed")
+        self.launches += 1
+        self._note_stream_write()
+
+    @_timed("norm")
+    def rmsnorm_add(self, h, delta, weight, eps, next_weight, next_eps, out):
+        """h += rmsnorm(delta) * weight (a norm behind a sublayer); with `next_weight` also
+        out = rmsnorm(h) * next_weight of the new stream, in the same kernel."""
+        self._rows(h), self._rows(delta)
+        check(self.lib.mb_rmsnorm_add(
+            _ptr(h), _ptr(delta), _flag(delta.dtype), _ptr(weight), _flag(weight.dtype), float(eps),
+            _ptr(next_weight), _flag(next_weight.dtype) if next_weight is not None else 0,
+            float(next_eps), _ptr(out), _flag(out.dtype) if out is not None else 0,
+            h.shape[0], h.shape[1], self._stream()), "rmsnorm_add")
         self.launches += 1
         self._note_stream_write()
 
@@ -485,6 +505,102 @@ class CudaOps:
         gate_up = ctx.buffer("gate_up", m, 2 * width)
         self.linear(x, weight, None, gate_up)
         self.swiglu(gate_up, out)
+
+    def linear_gated(self, x, weight, out, ctx, activation):
+        """out = act(x . gate^T) * (x . up^T) for `weight` = [gate rows; up rows]; "silu" takes
+        the fused kernels of `linear_swiglu`, "gelu_tanh" the product followed by the gate
+        kernel."""
+        if activation == "silu":
+            return self.linear_swiglu(x, weight, out, ctx)
+        if activation != "gelu_tanh":
+            raise KernelError(f"no gate kernel for the activation {activation!r}")
+        m, width = x.shape[0], out.shape[1]
+        gate_up = ctx.buffer("gate_up", m, 2 * width)
+        with self._as("gated product"):
+            self.linear(x, weight, None, gate_up)
+        self.gated_act(gate_up, out, 1)
+
+    @_timed("gate")
+    def gated_act(self, gate_up, out, act: int):
+        check(self.lib.mb_gated_act(_ptr(gate_up), _ptr(out), out.shape[0], out.shape[1],
+                                    _flag(out.dtype), int(act), self._stream()), "gated_act")
+        self.launches += 1
+
+    # ------------------------------------------------------------------ recurrent mixers
+
+    @_timed("recurrence")
+    def mingru_scan(self, pre, state, batch, out):
+        """pre [tokens, 3 * width] float32 = [z | u | g] before their activations; the state
+        [slots, width] float32 goes from token to token; out [tokens, width]."""
+        check(self.lib.mb_mingru_scan(_ptr(pre), _ptr(state), _ptr(batch.q_start), _ptr(batch.slots),
+                                      _ptr(out), batch.num_seqs, out.shape[1], _flag(out.dtype),
+                                      self._stream()), "mingru_scan")
+        self.launches += 1
+
+    @_timed("recurrence")
+    def causal_conv(self, pre, offset, width, taps_w, bias, state, batch, u):
+        """u = causal convolution per channel of the columns [offset, offset + width) of `pre`
+        (float32), the inputs from before the step taken from rows 1.. of the state
+        [slots, taps, width]."""
+        check(self.lib.mb_causal_conv(_ptr(pre), pre.shape[1], int(offset), _ptr(taps_w), _ptr(bias),
+                                      _ptr(state), _ptr(batch.q_start), _ptr(batch.slots),
+                                      _ptr(batch.seq_of_token), _ptr(u), u.shape[0], int(width),
+                                      taps_w.shape[1], self._stream()), "causal_conv")
+        self.launches += 1
+
+    @_timed("recurrence")
+    def block_gates(self, u, weight, bias, gates):
+        """gates [tokens, kinds * width] = sigmoid of the block-diagonal products of u
+        [tokens, width] with weight [kinds, blocks, in, out] + bias [kinds, blocks, out], all
+        float32 on the CUDA cores."""
+        kinds, blocks = weight.shape[0], weight.shape[1]
+        check(self.lib.mb_block_gates(_ptr(u), _ptr(weight), _ptr(bias), _ptr(gates), u.shape[0],
+                                      u.shape[1], blocks, kinds, self._stream()), "block_gates")
+        self.launches += 1
+
+    @_timed("recurrence")
+    def gated_recurrence_scan(self, pre, u, gates, softplus_lam, decay_scale, state, batch, out):
+        """S <- a S + sqrt(1 - a^2) i u with a = exp(-decay_scale * r * softplus_lam), out =
+        S * gelu_tanh(y); pre = [y | x], gates = [r | i]; the state's rows 1.. (the
+        convolution's past inputs) are brought up to the end of the step."""
+        check(self.lib.mb_gated_recurrence_scan(
+            _ptr(pre), _ptr(u), _ptr(gates), _ptr(softplus_lam), float(decay_scale), _ptr(state),
+            _ptr(batch.q_start), _ptr(batch.slots), _ptr(out), batch.num_seqs, out.shape[1],
+            state.shape[1], _flag(out.dtype), self._stream()), "gated_recurrence_scan")
+        self.launches += 1
+
+    # ------------------------------------------------------------------ mixed-head attention
+
+    @_timed("rotary + store")
+    def rope_blend_store(self, qkv, layout, tables, batch, cache, blend_from, blend, keep):
+        """Packed rows [q | k | v] with heads of (dim, dim, vdim): rotate the leading features
+        of q and k, copy v to `keep`, blend v with `blend_from` by the device scalar `blend`,
+        store k and v into the pages."""
+        heads, kv_heads, dim, vdim = layout
+        cos, sin = tables if tables is not None else (None, None)
+        rot = 2 * cos.shape[1] if cos is not None else 0
+        self._check_limits(cache, tables)
+        if cache.k.dtype != qkv.dtype:
+            raise KernelError("rope_blend_store: pages and activations differ in dtype")
+        check(self.lib.mb_rope_blend_store(
+            _ptr(qkv), _ptr(cos), _ptr(sin), rot, _ptr(batch.positions), _ptr(batch.seq_of_token),
+            _ptr(cache.table), cache.table.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(blend_from),
+            _ptr(blend), _ptr(keep), qkv.shape[0], heads, kv_heads, dim, vdim, cache.page_size,
+            int(cache.write), _flag(qkv.dtype), self._stream()), "rope_blend_store")
+        self.launches += 1
+
+    @_timed("attention")
+    def mixed_head_attention(self, qkv, layout, batch, cache, scale, window, mix, out):
+        """Attention over the pages whose heads' softmax weights are mixed by `mix`
+        [heads, heads] (float32, or None) before they meet the values."""
+        heads, kv_heads, dim, vdim = layout
+        self._check_limits(cache)
+        check(self.lib.mb_mixed_head_attention(
+            _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
+            cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(mix), _ptr(out),
+            batch.num_seqs, batch.max_q_len, heads, kv_heads, dim, vdim, cache.page_size,
+            float(scale), int(window), _flag(qkv.dtype), self._stream()), "mixed_head_attention")
+        self.launches += 1
 
     def qkv_rope_store(self, x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, tables,
                        batch, cache):

@@ -112,7 +112,9 @@ class GatedLinearRecurrence(Mixer):
         # what stands inside the recurrence is float32: taps, gate matrices, decay
         self.conv = place(n["conv"]).float().contiguous()
         self.conv_bias = place(n["conv"] + b).float().contiguous()
-        self.gate_weight = torch.stack([place(n["ra"]).float(), place(n["ri"]).float()]).contiguous()
+        # [2][blocks][in][out]: input-major, the way the gate kernel reads it
+        self.gate_weight = torch.stack([place(n["ra"]).float(), place(n["ri"]).float()]
+                                       ).transpose(-1, -2).contiguous()
         self.gate_bias = torch.stack([place(n["ra"] + b).float(), place(n["ri"] + b).float()]).contiguous()
         self.softplus_lam = torch.nn.functional.softplus(place(n["lam"]).float()).contiguous()
         self.out_weight = place(n["o"])

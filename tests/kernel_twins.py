@@ -135,10 +135,12 @@ class TorchOps:
             u[begin:end] = (acc + conv_bias.to(self.acc)).to(u.dtype)
 
     def block_gates(self, u, weight, bias, gates):
+        """weight [kinds][blocks][in][out], bias [kinds][blocks][out]; gates [tokens][kinds *
+        width] = sigmoid of the block-diagonal products."""
         kinds, blocks, size, _ = weight.shape
         ub = u.to(self.acc).view(u.shape[0], blocks, size)
         for kind in range(kinds):
-            pre = torch.einsum("boi,tbi->tbo", weight[kind].to(self.acc), ub) + bias[kind].to(self.acc)
+            pre = torch.einsum("bio,tbi->tbo", weight[kind].to(self.acc), ub) + bias[kind].to(self.acc)
             gates[:, kind * blocks * size:(kind + 1) * blocks * size] = \
                 torch.sigmoid(pre).reshape(u.shape[0], -1).to(gates.dtype)
 

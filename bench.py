@@ -521,6 +521,8 @@ def run_part(args) -> dict:
 
     if args.only == "mixed":
         return run_mixed(args)
+    if args.only == "designs":
+        return run_designs(args)
     raw = SIZES[args.size]
     _entry, config = config_from_dict(raw)
     vocab = raw["vocab_size"]
@@ -599,6 +601,158 @@ def run_part(args) -> dict:
                                                args.warmup)
     return {"decode_tokens_per_s": round(rate, 1), "ms_per_step": round(ms, 4), "batch": batch,
             "launches_per_step": launches, "graphs": not args.no_graphs}
+
+
+# ------------------------------------------------------------------------------ other designs
+
+DESIGN_SIZES = {
+    # width, query heads, key/value heads, head size, feed-forward, recurrent blocks
+    "0.5b": (896, 14, 2, 64, 4864, 7),
+    "1.5b": (1536, 12, 2, 128, 8960, 12),
+}
+DESIGN_LAYERS = 8
+DESIGN_VOCAB = 32768
+
+
+def design_configs(size: str) -> tuple[dict, dict]:
+    """A Fegenex model at the layer sizes of `size` (attention with a feed-forward, minGRU,
+    gated linear recurrence, attention with a feed-forward, twice over) and the Qwen2 model
+    of the same width, heads, feed-forward, depth and vocabulary beside it."""
+    width, heads, kv_heads, dim, ff, blocks = DESIGN_SIZES[size]
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+                 "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
+                           "rot": {"dims": dim // 2, "base": 10000.0}, "scale": dim ** -0.5,
+                           "v_mix": True}}
+    order = [attention, {"type": "mingru", "mixer": {"width": width}, "mlp": None},
+             {"type": "rglru", "mixer": {"width": width, "blocks": blocks, "conv": 4}, "mlp": None},
+             attention]
+    fegenex = {"architecture": "Fegenex", "width": width, "vocab": DESIGN_VOCAB,
+               "max_positions": MODEL_LEN, "norm": {"eps": 1e-6},
+               "layers": [order[i % len(order)] for i in range(DESIGN_LAYERS)]}
+    qwen2 = {**SIZES[size], "num_hidden_layers": DESIGN_LAYERS, "vocab_size": DESIGN_VOCAB,
+             "tie_word_embeddings": False}
+    return fegenex, qwen2
+
+
+def design_costs(raw: dict, batch: int, context: int, tokens: int) -> dict:
+    """Per class of kernel call, what a Fegenex model has to read (decode step, bytes) or
+    compute (prompt step, flops; bytes for the classes that only move data)."""
+    w, v = raw["width"], raw["vocab"]
+    products = head = 2 * v * w
+    gated = kv_token = att_flops = mix_flops = rec_tokens = 0
+    norms = 1
+    for layer in raw["layers"]:
+        m = layer["mixer"]
+        norms += 2
+        if layer["type"] == "attention":
+            qkv = (m["heads"] + m["kv_heads"]) * m["dim"] + m["kv_heads"] * m["vdim"]
+            products += 2 * (qkv * w + m["heads"] * m["vdim"] * w)
+            kv_token += 2 * m["kv_heads"] * (m["dim"] + m["vdim"])
+            att_flops += m["heads"] * (m["dim"] + m["vdim"])
+            mix_flops += m["heads"] * m["heads"]
+        elif layer["type"] == "mingru":
+            products += 2 * 4 * m["width"] * w
+            rec_tokens += 4 * 3 * m["width"] + 2 * m["width"]
+        else:
+            products += 2 * 3 * m["width"] * w
+            rec_tokens += 4 * 9 * m["width"] + 2 * m["width"]
+        if layer["mlp"]:
+            norms += 2
+            gated += 2 * 2 * layer["mlp"]["ff"] * w
+            products += 2 * layer["mlp"]["ff"] * w
+    t = tokens
+    return {
+        "decode": {"product": ("hbm", products), "gated product": ("hbm", gated),
+                   "attention": ("hbm", batch * context * kv_token),
+                   "recurrence": ("hbm", batch * rec_tokens), "norm": ("hbm", norms * batch * w * 12)},
+        "prefill": {"product": ("tensor", t * (products - head) + head),
+                    "gated product": ("tensor", t * gated),
+                    "attention": ("tensor", t * t * (att_flops + mix_flops)),
+                    "recurrence": ("hbm", t * rec_tokens), "norm": ("hbm", norms * t * w * 14)},
+    }
+
+
+def classes_of(torch, runner, batch, context, vocab, costs, peak) -> dict:
+    """Milliseconds per class of kernel call of a decode step and of a prompt step (events
+    around every call, the launches queued behind a delay on the device), with the fraction
+    of the measured peak where `costs` names what the class has to do."""
+    from mercury_b200.engine.batch import StepEntry
+
+    seqs = fill_contexts(torch, runner, batch, context, vocab)
+    gen = torch.Generator().manual_seed(SEED + 6)
+    tokens = torch.randint(0, vocab, (4, batch), generator=gen).tolist()
+    prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+    runner.time_kernels = True
+    try:
+        rows = []
+        for turn in range(4):
+            torch.cuda._sleep(20_000_000)
+            runner.step([StepEntry(s, [tokens[turn][i]], [0]) for i, s in enumerate(seqs)])
+            rows.append(dict(runner.last_kernel_ms))
+        decode = {k: statistics.median(r.get(k, 0.0) for r in rows[2:]) for k in rows[-1]}
+        for s in seqs:
+            runner.close(s)
+        rows = []
+        for turn in range(3):
+            seq = runner.open(f"classes-{turn}")
+            torch.cuda._sleep(40_000_000)
+            runner.step([StepEntry(seq, prompt, [PREFILL_TOKENS - 1])])
+            rows.append(dict(runner.last_kernel_ms))
+            runner.close(seq)
+        prefill = {k: statistics.median(r.get(k, 0.0) for r in rows[1:]) for k in rows[-1]}
+    finally:
+        runner.time_kernels = False
+    out = {}
+    for name, measured in (("decode", decode), ("prefill", prefill)):
+        block = {}
+        for kind, ms in sorted(measured.items()):
+            bound, amount = costs[name].get(kind, ("hbm", 0))
+            top = peak["hbm_gbs"] * 1e9 if bound == "hbm" else peak["bf16_tflops"] * 1e12
+            block[kind] = {"ms": round(ms, 4), "bound": bound,
+                           "frac": round(amount / (ms * 1e-3) / top, 4) if ms > 0 and amount else None}
+        block["sum_ms"] = round(sum(measured.values()), 4)
+        out[name] = block
+    return out
+
+
+def run_designs(args) -> dict:
+    """`--only designs`: prefill and decode throughput of Fegenex at a few layer sizes of
+    real models (random weights, 8 layers), beside Qwen2 at the same sizes, with every
+    class of kernel call against its roofline."""
+    import torch
+
+    from mercury_b200.config import config_from_dict
+    from mercury_b200.weights import random_tensors
+
+    peak, peak_kind = peaks()
+    out = {"workload": f"{DESIGN_LAYERS} layers, vocabulary {DESIGN_VOCAB}, decode batch {args.batch} "
+                       f"at {CONTEXT}-token contexts, prompt of {PREFILL_TOKENS} tokens, bfloat16",
+           "peaks": peak_kind, "sizes": {}}
+    for size in ([args.size] if args.size_given else list(DESIGN_SIZES)):
+        row = {}
+        fegenex, qwen2 = design_configs(size)
+        for label, raw in (("fegenex", fegenex), ("qwen2", qwen2)):
+            _entry, config = config_from_dict(raw)
+            tensors = random_tensors(config, SEED, torch.bfloat16)
+            vocab = DESIGN_VOCAB
+            batch = args.batch
+            runner = make_runner(torch, config, tensors, max(batch, 2),
+                                 max(batch, 2) * (CONTEXT + 256), graphs=not args.no_graphs)
+            prefill_ms = prefill_rate(torch, runner, vocab)
+            rate, ms, launches, _ = decode_rate(torch, runner, batch, CONTEXT, vocab, args.steps,
+                                                max(3, args.warmup))
+            costs = (design_costs(raw, batch, CONTEXT, PREFILL_TOKENS) if label == "fegenex"
+                     else class_costs(raw, batch, CONTEXT, PREFILL_TOKENS))
+            row[label] = {"prefill_ms": round(prefill_ms, 3),
+                          "prefill_tokens_per_s": round(PREFILL_TOKENS / prefill_ms * 1e3, 1),
+                          "decode_ms_per_step": round(ms, 4), "decode_tokens_per_s": round(rate, 1),
+                          "launches_per_decode_step": launches,
+                          "classes": classes_of(torch, runner, batch, CONTEXT, vocab, costs, peak)}
+            del runner, tensors
+            torch.cuda.empty_cache()
+        out["sizes"][size] = row
+    return out
+
 
 
 def run_mixed(args, prepared=None) -> dict:
@@ -732,7 +886,7 @@ def main() -> int:
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="mercury_b200", choices=("mercury_b200", "reference"))
     p.add_argument("--only", default="all",
-                   choices=("all", "decode", "prefill", "products", "mixed", "kernels"),
+                   choices=("all", "decode", "prefill", "products", "mixed", "kernels", "designs"),
                    help="run one part only (for profilers and side workloads); prints its own JSON")
     p.add_argument("--size", default=None, choices=tuple(SIZES),
                    help="layer sizes of --only decode/prefill/mixed (default 0.5b; mixed: 1.5b)")
@@ -747,6 +901,7 @@ def main() -> int:
     if args.gpus != 1:
         print("bench.py measures a single-GPU engine; --gpus must be 1", flush=True)
         return 2
+    args.size_given = args.size is not None
     if args.size is None:
         args.size = "1.5b" if args.only == "mixed" else "0.5b"
     if args.only != "all":

@@ -36,6 +36,14 @@ struct MixedAttentionArgs {
     int n_q, n_kv, d, vd, page_size;
     float scale;
     int window, tiles_per_seq, bq;
+    // The keys of a row tile may be divided over gridDim.y blocks (decode-like batches that
+    // would otherwise leave most SMs idle). mode 0: one block does everything. mode 1: a
+    // block leaves its range's (maximum, sum) per row in part_ml. mode 2: a block merges the
+    // ranges' (maximum, sum), weighs its own range with the finished softmax and leaves its
+    // share of the output in part_out, which mixed_head_sum_kernel adds up in a fixed order.
+    int num_splits, mode;
+    float* part_ml;         // [tokens][n_q][splits][2]
+    float* part_out;        // [tokens][n_q][splits][vd]
 };
 
 template <typename T, int NC>
@@ -85,7 +93,12 @@ mixed_head_attention_kernel(const MixedAttentionArgs a) {
     const int p_min = first_pos + tok0, p_max = first_pos + tok0 + n_tok - 1;
     int t_lo = 0;
     if (a.window > 0 && p_min - a.window + 1 > 0) t_lo = (p_min - a.window + 1) / MH_KEYS;
-    const int t_hi = p_max / MH_KEYS + 1;
+    int t_hi = p_max / MH_KEYS + 1;
+    if (a.num_splits > 1) {
+        const int per = (t_hi - t_lo + a.num_splits - 1) / a.num_splits;
+        t_lo += (int)blockIdx.y * per;
+        if (t_lo + per < t_hi) t_hi = t_lo + per;
+    }
 
     // this warp's rows
     int row_pos[MH_RPW];
@@ -109,7 +122,25 @@ mixed_head_attention_kernel(const MixedAttentionArgs a) {
 #pragma unroll
         for (int n = 0; n < NC; ++n) acc[k][n] = 0.f;
 
-    for (int pass = 0; pass < 2; ++pass) {
+    if (a.mode == 2) {
+        // the finished maximum and sum of each row, from every range's share
+#pragma unroll
+        for (int k = 0; k < MH_RPW; ++k) {
+            if (!row_ok[k]) continue;
+            const int r = warp + MH_WARPS * k;
+            const int h = r / bq, i = r - h * bq;
+            const float* ml = a.part_ml + ((int64_t)(q_begin + tok0 + i) * H + h) * a.num_splits * 2;
+            float big = -INFINITY;
+            for (int z = 0; z < a.num_splits; ++z) big = fmaxf(big, ml[2 * z]);
+            float sum = 0.f;
+            for (int z = 0; z < a.num_splits; ++z)
+                if (ml[2 * z] > -INFINITY) sum += ml[2 * z + 1] * expf(ml[2 * z] - big);
+            row_m[k] = big;
+            row_l[k] = sum;
+        }
+    }
+    const int pass_begin = a.mode == 2 ? 1 : 0, pass_end = a.mode == 1 ? 1 : 2;
+    for (int pass = pass_begin; pass < pass_end; ++pass) {
         if (pass == 1) {
 #pragma unroll
             for (int k = 0; k < MH_RPW; ++k) row_l[k] = row_l[k] > 0.f ? 1.f / row_l[k] : 0.f;
@@ -259,6 +290,28 @@ mixed_head_attention_kernel(const MixedAttentionArgs a) {
         }
     }
 
+    if (a.mode != 0) {
+#pragma unroll
+        for (int k = 0; k < MH_RPW; ++k) {
+            if (!row_ok[k]) continue;
+            const int r = warp + MH_WARPS * k;
+            const int h = r / bq, i = r - h * bq;
+            const int64_t at = ((int64_t)(q_begin + tok0 + i) * H + h) * a.num_splits + blockIdx.y;
+            if (a.mode == 1) {
+                if (lane == 0) {
+                    a.part_ml[at * 2] = row_m[k];
+                    a.part_ml[at * 2 + 1] = row_l[k];
+                }
+                continue;
+            }
+#pragma unroll
+            for (int n = 0; n < NC; ++n) {
+                const int f = n * 32 + lane;
+                if (f < vd) a.part_out[at * vd + f] = acc[k][n];
+            }
+        }
+        return;
+    }
     T* out = reinterpret_cast<T*>(a.out);
 #pragma unroll
     for (int k = 0; k < MH_RPW; ++k) {
@@ -274,6 +327,23 @@ mixed_head_attention_kernel(const MixedAttentionArgs a) {
     }
 }
 
+// out[token][head][:] = sum over the ranges, in ascending order; padding tokens get zeros.
+template <typename T>
+__global__ void mixed_head_sum_kernel(const float* __restrict__ part_out,
+                                      const int* __restrict__ seq_of_token, T* __restrict__ out,
+                                      int n_q, int vd, int num_splits) {
+    grid_dependency_sync();
+    const int tok = blockIdx.x, head = blockIdx.y;
+    const int64_t flat = (int64_t)tok * n_q + head;
+    const bool live = seq_of_token[tok] >= 0;
+    for (int f = threadIdx.x; f < vd; f += blockDim.x) {
+        float v = 0.f;
+        if (live)
+            for (int z = 0; z < num_splits; ++z) v += part_out[(flat * num_splits + z) * vd + f];
+        out[flat * vd + f] = from_float<T>(v);
+    }
+}
+
 template <typename T, int NC>
 int launch_mixed_attention(const MixedAttentionArgs& a, int num_seqs, cudaStream_t s) {
     const size_t smem = (size_t)(MH_ROWS * a.d + MH_KEYS * (a.d + 1) + MH_KEYS * NC * 32 +
@@ -286,7 +356,8 @@ int launch_mixed_attention(const MixedAttentionArgs& a, int num_seqs, cudaStream
             return MB_ERR_UNSUPPORTED_SIZE;
         raised = smem;
     }
-    MB_LAUNCH((mixed_head_attention_kernel<T, NC>), num_seqs * a.tiles_per_seq, MH_WARPS * 32, smem, s, a);
+    dim3 grid(num_seqs * a.tiles_per_seq, a.num_splits);
+    MB_LAUNCH((mixed_head_attention_kernel<T, NC>), grid, MH_WARPS * 32, smem, s, a);
     return launch_status();
 }
 
@@ -377,12 +448,19 @@ __global__ void rope_blend_store_kernel(T* __restrict__ qkv, const float* __rest
 
 using namespace mb;
 
+// Floats of scratch that `num_splits` ranges need for `tokens` rows of the batch.
+MB_EXPORT long long mb_mixed_head_scratch_floats(int tokens, int n_q, int vd, int num_splits) {
+    return num_splits <= 1 ? 0 : (long long)tokens * n_q * num_splits * (vd + 2);
+}
+
 MB_EXPORT int mb_mixed_head_attention(const void* qkv, int row_width, const void* k_pages,
                                       const void* v_pages, const int* table, int max_pages,
                                       const int* q_start, const int* kv_len, const float* mix,
                                       void* out, int num_seqs, int max_q_len, int n_q, int n_kv,
                                       int d, int vd, int page_size, float scale, int window,
-                                      int dtype, void* stream) {
+                                      int dtype, int num_splits, const int* seq_of_token,
+                                      int tokens, float* scratch, long long scratch_floats,
+                                      void* stream) {
     if (num_seqs <= 0 || max_q_len <= 0) return MB_OK;
     if (d <= 0 || d > 256 || vd <= 0 || vd > 256 || n_kv <= 0 || n_q % n_kv || n_q > MH_ROWS)
         return MB_ERR_UNSUPPORTED_SIZE;
@@ -397,10 +475,34 @@ MB_EXPORT int mb_mixed_head_attention(const void* qkv, int row_width, const void
     if (bq > max_q_len) bq = max_q_len;
     a.bq = bq;
     a.tiles_per_seq = (max_q_len + bq - 1) / bq;
+    a.num_splits = 1;
+    a.mode = 0;
+    a.part_ml = a.part_out = nullptr;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == MB_F32) return dispatch_mixed_attention<float>(a, num_seqs, s);
-    if (dtype == MB_BF16) return dispatch_mixed_attention<__nv_bfloat16>(a, num_seqs, s);
-    return MB_ERR_BAD_DTYPE;
+    if (dtype != MB_F32 && dtype != MB_BF16) return MB_ERR_BAD_DTYPE;
+    if (num_splits <= 1)
+        return dtype == MB_F32 ? dispatch_mixed_attention<float>(a, num_seqs, s)
+                               : dispatch_mixed_attention<__nv_bfloat16>(a, num_seqs, s);
+    if (num_splits > 65535 || n_q > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    if (!scratch || scratch_floats < mb_mixed_head_scratch_floats(tokens, n_q, vd, num_splits))
+        return MB_ERR_SCRATCH;
+    a.num_splits = num_splits;
+    a.part_out = scratch;
+    a.part_ml = scratch + (int64_t)tokens * n_q * num_splits * vd;
+    for (int mode = 1; mode <= 2; ++mode) {
+        a.mode = mode;
+        const int rc = dtype == MB_F32 ? dispatch_mixed_attention<float>(a, num_seqs, s)
+                                       : dispatch_mixed_attention<__nv_bfloat16>(a, num_seqs, s);
+        if (rc != MB_OK) return rc;
+    }
+    dim3 grid(tokens, n_q);
+    if (dtype == MB_F32)
+        MB_LAUNCH((mixed_head_sum_kernel<float>), grid, 64, 0, s, (const float*)a.part_out, seq_of_token,
+                  (float*)out, n_q, vd, num_splits);
+    else
+        MB_LAUNCH((mixed_head_sum_kernel<__nv_bfloat16>), grid, 64, 0, s, (const float*)a.part_out,
+                  seq_of_token, (__nv_bfloat16*)out, n_q, vd, num_splits);
+    return launch_status();
 }
 
 MB_EXPORT int mb_rope_blend_store(void* qkv, const float* cos_t, const float* sin_t, int rot,

@@ -82,7 +82,8 @@ _SIGNATURES = {
     "mb_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "mb_mixed_head_attention": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                c_int, c_int, c_float, c_int, c_int, c_void_p],
+                                c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_int,
+                                c_void_p, c_longlong, c_void_p],
     "mb_rope_blend_store": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                             c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -133,6 +134,8 @@ def load():
     lib.mb_attention_decode_raw_pays.restype = c_int
     lib.mb_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mb_attention_scratch_floats.restype = c_longlong
+    lib.mb_mixed_head_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mb_mixed_head_scratch_floats.restype = c_longlong
     _LIB = lib
     return lib
 

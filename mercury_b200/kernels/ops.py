@@ -595,12 +595,36 @@ class CudaOps:
         [heads, heads] (float32, or None) before they meet the values."""
         heads, kv_heads, dim, vdim = layout
         self._check_limits(cache)
+        tokens = qkv.shape[0]
+        splits = self._mixed_head_splits(batch, heads)
+        floats = self.lib.mb_mixed_head_scratch_floats(tokens, heads, vdim, splits)
+        scratch = self._scratch_for(floats) if floats else None
         check(self.lib.mb_mixed_head_attention(
             _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
             cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(mix), _ptr(out),
             batch.num_seqs, batch.max_q_len, heads, kv_heads, dim, vdim, cache.page_size,
-            float(scale), int(window), _flag(qkv.dtype), self._stream()), "mixed_head_attention")
-        self.launches += 1
+            float(scale), int(window), _flag(qkv.dtype), splits, _ptr(batch.seq_of_token), tokens,
+            _ptr(scratch), scratch.numel() if scratch is not None else 0, self._stream()),
+            "mixed_head_attention")
+        self.launches += 1 if splits == 1 else 3
+
+    def _mixed_head_splits(self, batch, heads: int) -> int:
+        """Key ranges per row tile of the mixed-head attention: one block holds every head of
+        a tile of tokens, so a decode step brings one block per sequence, and its keys are
+        divided until the device is about filled. Inside a captured step (the batch names
+        `attention_splits`) the count depends on the batch's shape only, never on its
+        lengths; a block whose range is empty leaves zeros."""
+        if self.decode_splits is not None:
+            return max(1, self.decode_splits)
+        bq = max(1, min(64 // heads, 16, batch.max_q_len))
+        blocks = batch.num_seqs * -(-batch.max_q_len // bq)
+        if blocks >= self.sm_count:
+            return 1
+        fill = min(64, -(-2 * self.sm_count // blocks))
+        if getattr(batch, "attention_splits", None):
+            return fill
+        key_tiles = -(-batch.max_kv_len // 32)
+        return max(1, min(fill, key_tiles // 4))
 
     def qkv_rope_store(self, x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, tables,
                        batch, cache):

@@ -190,9 +190,15 @@ def fill_pages(table, kv_lens, q_lens, n_kv, d, vd, page, num_pages, dtype, seed
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("splits", [1, 3, 7])
 @pytest.mark.parametrize("case", range(len(MIXED_CASES)), ids=lambda i: f"case{i}")
-def test_rotate_blend_store_and_attend(ops, twin, dtype, case):
+def test_rotate_blend_store_and_attend(twin, dtype, splits, case):
+    """`splits`: the keys of a row tile divided over that many blocks (some of them with no
+    key at all when the sequence is short), merged afterwards."""
+    from mercury_b200.kernels.ops import CudaOps
     from test_kernels_gpu import make_batch
+
+    ops = CudaOps("cuda", decode_splits=splits)
 
     heads, kv_heads, d, vd, rot, page, q_lens, kv_lens, window, use_mix = MIXED_CASES[case]
     num_pages = sum(-(-kv // page) for kv in kv_lens) + 3

@@ -15,31 +15,88 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// ---- the scan ----------------------------------------------------------------------------
+// Both recurrences are S_t = a_t S_{t-1} + b_t per channel, with a_t, b_t read off the
+// token alone. A block takes 32 channels of one sequence and cuts the step's tokens into
+// blockDim.y runs: every thread first folds its run into (A, B) with S_end = A S_start + B,
+// one thread per channel chains the runs' starts, and every thread then walks its run again
+// from its start and writes the outputs. The state that goes on to the next step is the
+// last run's own final value. A decode step (one token) is a single run.
+constexpr int SC_CHANNELS = 32;
+constexpr int SC_MAX_RUNS = 32;
+
+template <typename T, typename F>
+__device__ __forceinline__ void scan_runs(const F& f, float* cell, int begin, int end, int c,
+                                          bool live, T* __restrict__ out, int width) {
+    __shared__ float run_a[SC_MAX_RUNS][SC_CHANNELS], run_b[SC_MAX_RUNS][SC_CHANNELS];
+    const int runs = blockDim.y, k = threadIdx.y, x = threadIdx.x;
+    const int n = end - begin;
+    const int len = (n + runs - 1) / runs;
+    const int t0 = min(end, begin + k * len), t1 = min(end, t0 + len);
+    if (runs > 1) {
+        float A = 1.f, B = 0.f;
+        if (live)
+            for (int t = t0; t < t1; ++t) {
+                float a, b, o;
+                f(t, c, a, b, o);
+                B = a * B + b;
+                A *= a;
+            }
+        run_a[k][x] = A;
+        run_b[k][x] = B;
+        __syncthreads();
+        if (k == 0 && live) {
+            float s = *cell;
+            for (int j = 0; j < runs; ++j) {
+                const float A2 = run_a[j][x], B2 = run_b[j][x];
+                run_a[j][x] = s;                 // the run's start
+                s = A2 * s + B2;
+            }
+        }
+        __syncthreads();
+    }
+    if (!live || t0 >= t1) return;
+    float s = runs > 1 ? run_a[k][x] : *cell;
+#pragma unroll 4
+    for (int t = t0; t < t1; ++t) {
+        float a, b, o;
+        f(t, c, a, b, o);
+        s = a * s + b;
+        out[(int64_t)t * width + c] = from_float<T>(s * o);
+    }
+    if (t1 == end) *cell = s;
+}
+
 // pre: [tokens][3 * width] float32 = [gate z | candidate u | output gate g] before their
 // activations. S <- (1 - z) S + z c with z = sigmoid(.), c = u + 1/2 (u >= 0) or sigmoid(u);
 // out = S * silu(g).
-template <typename T>
-__global__ void mingru_scan_kernel(const float* __restrict__ pre, float* __restrict__ state,
-                                   const int* __restrict__ q_start, const int* __restrict__ slots,
-                                   T* __restrict__ out, int width) {
-    grid_dependency_sync();
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    const int seq = blockIdx.y;
-    const int begin = q_start[seq], end = q_start[seq + 1];
-    if (c >= width || begin >= end) return;
-    float* cell = state + (int64_t)slots[seq] * width + c;
-    float s = *cell;
-#pragma unroll 4
-    for (int t = begin; t < end; ++t) {
+struct MinGruStep {
+    const float* pre;
+    int width;
+    __device__ __forceinline__ void operator()(int t, int c, float& a, float& b, float& o) const {
         const float* row = pre + (int64_t)t * 3 * width;
         const float z = sigmoid_f(row[c]);
         const float u = row[width + c];
         const float g = row[2 * width + c];
-        const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-        s = (1.f - z) * s + z * cand;
-        out[(int64_t)t * width + c] = from_float<T>(s * (g * sigmoid_f(g)));
+        a = 1.f - z;
+        b = z * (u >= 0.f ? u + 0.5f : sigmoid_f(u));
+        o = g * sigmoid_f(g);
     }
-    *cell = s;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(SC_CHANNELS * SC_MAX_RUNS)
+mingru_scan_kernel(const float* __restrict__ pre, float* __restrict__ state,
+                   const int* __restrict__ q_start, const int* __restrict__ slots,
+                   T* __restrict__ out, int width) {
+    grid_dependency_sync();
+    const int c = blockIdx.x * SC_CHANNELS + threadIdx.x;
+    const int seq = blockIdx.y;
+    const int begin = q_start[seq], end = q_start[seq + 1];
+    if (begin >= end) return;
+    const bool live = c < width;
+    MinGruStep f{pre, width};
+    scan_runs<T>(f, state + (int64_t)slots[seq] * width + (live ? c : 0), begin, end, c, live, out, width);
 }
 
 // u[t][c] = sum_k taps_w[c][k] * x[t - (taps - 1 - k)][c] + bias[c], x = pre[:, offset + c]
@@ -115,56 +172,73 @@ block_gates_kernel(const float* __restrict__ u, const float* __restrict__ w,
 // a = exp(-decay_scale * r * softplus_lam), S <- a S + sqrt(1 - a^2) * i * u, out = S * gelu(y).
 // state[slot]: row 0 = S, row j = the convolution's input j tokens back; the rows 1.. are
 // brought up to the end of this step here, after every token's convolution has been taken.
-template <typename T>
-__global__ void gated_recurrence_scan_kernel(const float* __restrict__ pre, const float* __restrict__ u,
-                                             const float* __restrict__ gates,
-                                             const float* __restrict__ softplus_lam, float decay_scale,
-                                             float* __restrict__ state, const int* __restrict__ q_start,
-                                             const int* __restrict__ slots, T* __restrict__ out,
-                                             int width, int taps) {
-    grid_dependency_sync();
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    const int seq = blockIdx.y;
-    const int begin = q_start[seq], end = q_start[seq + 1];
-    if (c >= width || begin >= end) return;
-    float* mine = state + (int64_t)slots[seq] * taps * width + c;
-    const float sp = softplus_lam[c];
-    float s = mine[0];
-#pragma unroll 4
-    for (int t = begin; t < end; ++t) {
+struct GatedStep {
+    const float* pre;
+    const float* u;
+    const float* gates;
+    const float* softplus_lam;
+    float decay_scale;
+    int width;
+    __device__ __forceinline__ void operator()(int t, int c, float& a, float& b, float& o) const {
         const float r = gates[(int64_t)t * 2 * width + c];
         const float i = gates[(int64_t)t * 2 * width + width + c];
-        const float x = u[(int64_t)t * width + c];
-        const float y = pre[(int64_t)t * 2 * width + c];
-        const float a = expf(-decay_scale * r * sp);
-        s = a * s + sqrtf(1.f - a * a) * i * x;
-        out[(int64_t)t * width + c] = from_float<T>(s * gelu_tanh_f(y));
+        a = expf(-decay_scale * r * softplus_lam[c]);
+        b = sqrtf(1.f - a * a) * i * u[(int64_t)t * width + c];
+        o = gelu_tanh_f(pre[(int64_t)t * 2 * width + c]);
     }
-    mine[0] = s;
-    const int n = end - begin;
-    float old[16];
-    for (int j = 1; j < taps; ++j) old[j] = mine[(int64_t)j * width];
-    for (int j = 1; j < taps; ++j) {
-        const int idx = n - j;
-        mine[(int64_t)j * width] =
-            idx >= 0 ? pre[(int64_t)(begin + idx) * 2 * width + width + c] : old[j - n];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(SC_CHANNELS * SC_MAX_RUNS)
+gated_recurrence_scan_kernel(const float* __restrict__ pre, const float* __restrict__ u,
+                             const float* __restrict__ gates, const float* __restrict__ softplus_lam,
+                             float decay_scale, float* __restrict__ state,
+                             const int* __restrict__ q_start, const int* __restrict__ slots,
+                             T* __restrict__ out, int width, int taps) {
+    grid_dependency_sync();
+    const int c = blockIdx.x * SC_CHANNELS + threadIdx.x;
+    const int seq = blockIdx.y;
+    const int begin = q_start[seq], end = q_start[seq + 1];
+    if (begin >= end) return;
+    const bool live = c < width;
+    float* mine = state + (int64_t)slots[seq] * taps * width + (live ? c : 0);
+    if (live && threadIdx.y == 0) {
+        const int n = end - begin;
+        float old[16];
+        for (int j = 1; j < taps; ++j) old[j] = mine[(int64_t)j * width];
+        for (int j = 1; j < taps; ++j) {
+            const int idx = n - j;
+            mine[(int64_t)j * width] =
+                idx >= 0 ? pre[(int64_t)(begin + idx) * 2 * width + width + c] : old[j - n];
+        }
     }
+    GatedStep f{pre, u, gates, softplus_lam, decay_scale, width};
+    scan_runs<T>(f, mine, begin, end, c, live, out, width);
 }
 
 }  // namespace mb
 
 using namespace mb;
 
+// Runs per sequence for a step whose longest portion has `max_q_len` tokens: about 16
+// tokens per run, at most SC_MAX_RUNS.
+static int scan_run_count(int max_q_len) {
+    int runs = (max_q_len + 15) / 16;
+    return runs < 1 ? 1 : (runs > SC_MAX_RUNS ? SC_MAX_RUNS : runs);
+}
+
 MB_EXPORT int mb_mingru_scan(const float* pre, float* state, const int* q_start, const int* slots,
-                             void* out, int num_seqs, int width, int dtype, void* stream) {
+                             void* out, int num_seqs, int max_q_len, int width, int dtype,
+                             void* stream) {
     if (num_seqs <= 0 || width <= 0) return MB_OK;
     if (num_seqs > 65535) return MB_ERR_UNSUPPORTED_SIZE;
-    dim3 grid((width + 127) / 128, num_seqs);
+    dim3 grid((width + SC_CHANNELS - 1) / SC_CHANNELS, num_seqs);
+    dim3 block(SC_CHANNELS, scan_run_count(max_q_len));
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MB_F32)
-        MB_LAUNCH((mingru_scan_kernel<float>), grid, 128, 0, s, pre, state, q_start, slots, (float*)out, width);
+        MB_LAUNCH((mingru_scan_kernel<float>), grid, block, 0, s, pre, state, q_start, slots, (float*)out, width);
     else if (dtype == MB_BF16)
-        MB_LAUNCH((mingru_scan_kernel<__nv_bfloat16>), grid, 128, 0, s, pre, state, q_start, slots,
+        MB_LAUNCH((mingru_scan_kernel<__nv_bfloat16>), grid, block, 0, s, pre, state, q_start, slots,
                   (__nv_bfloat16*)out, width);
     else
         return MB_ERR_BAD_DTYPE;
@@ -209,16 +283,18 @@ MB_EXPORT int mb_block_gates(const float* u, const float* w, const float* bias, 
 MB_EXPORT int mb_gated_recurrence_scan(const float* pre, const float* u, const float* gates,
                                        const float* softplus_lam, float decay_scale, float* state,
                                        const int* q_start, const int* slots, void* out,
-                                       int num_seqs, int width, int taps, int dtype, void* stream) {
+                                       int num_seqs, int max_q_len, int width, int taps, int dtype,
+                                       void* stream) {
     if (num_seqs <= 0 || width <= 0) return MB_OK;
     if (taps < 1 || taps > 16 || num_seqs > 65535) return MB_ERR_UNSUPPORTED_SIZE;
-    dim3 grid((width + 127) / 128, num_seqs);
+    dim3 grid((width + SC_CHANNELS - 1) / SC_CHANNELS, num_seqs);
+    dim3 block(SC_CHANNELS, scan_run_count(max_q_len));
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MB_F32)
-        MB_LAUNCH((gated_recurrence_scan_kernel<float>), grid, 128, 0, s, pre, u, gates, softplus_lam,
+        MB_LAUNCH((gated_recurrence_scan_kernel<float>), grid, block, 0, s, pre, u, gates, softplus_lam,
                   decay_scale, state, q_start, slots, (float*)out, width, taps);
     else if (dtype == MB_BF16)
-        MB_LAUNCH((gated_recurrence_scan_kernel<__nv_bfloat16>), grid, 128, 0, s, pre, u, gates,
+        MB_LAUNCH((gated_recurrence_scan_kernel<__nv_bfloat16>), grid, block, 0, s, pre, u, gates,
                   softplus_lam, decay_scale, state, q_start, slots, (__nv_bfloat16*)out, width, taps);
     else
         return MB_ERR_BAD_DTYPE;

@@ -87,12 +87,13 @@ _SIGNATURES = {
     "mb_rope_blend_store": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                             c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "mb_mingru_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "mb_mingru_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                       c_void_p],
     "mb_causal_conv": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_block_gates": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "mb_gated_recurrence_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
-                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "mb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }

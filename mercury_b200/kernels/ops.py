@@ -533,8 +533,8 @@ class CudaOps:
         """pre [tokens, 3 * width] float32 = [z | u | g] before their activations; the state
         [slots, width] float32 goes from token to token; out [tokens, width]."""
         check(self.lib.mb_mingru_scan(_ptr(pre), _ptr(state), _ptr(batch.q_start), _ptr(batch.slots),
-                                      _ptr(out), batch.num_seqs, out.shape[1], _flag(out.dtype),
-                                      self._stream()), "mingru_scan")
+                                      _ptr(out), batch.num_seqs, batch.max_q_len, out.shape[1],
+                                      _flag(out.dtype), self._stream()), "mingru_scan")
         self.launches += 1
 
     @_timed("recurrence")
@@ -565,8 +565,8 @@ class CudaOps:
         convolution's past inputs) are brought up to the end of the step."""
         check(self.lib.mb_gated_recurrence_scan(
             _ptr(pre), _ptr(u), _ptr(gates), _ptr(softplus_lam), float(decay_scale), _ptr(state),
-            _ptr(batch.q_start), _ptr(batch.slots), _ptr(out), batch.num_seqs, out.shape[1],
-            state.shape[1], _flag(out.dtype), self._stream()), "gated_recurrence_scan")
+            _ptr(batch.q_start), _ptr(batch.slots), _ptr(out), batch.num_seqs, batch.max_q_len,
+            out.shape[1], state.shape[1], _flag(out.dtype), self._stream()), "gated_recurrence_scan")
         self.launches += 1
 
     # ------------------------------------------------------------------ mixed-head attention

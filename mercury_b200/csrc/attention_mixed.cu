@@ -344,6 +344,18 @@ __global__ void mixed_head_sum_kernel(const float* __restrict__ part_out,
     }
 }
 
+int launch_mixed_head_sum(const float* part_out, const int* seq_of_token, void* out, int tokens,
+                          int n_q, int vd, int num_splits, int dtype, cudaStream_t s) {
+    dim3 grid(tokens, n_q);
+    if (dtype == MB_F32)
+        MB_LAUNCH((mixed_head_sum_kernel<float>), grid, 64, 0, s, part_out, seq_of_token, (float*)out,
+                  n_q, vd, num_splits);
+    else
+        MB_LAUNCH((mixed_head_sum_kernel<__nv_bfloat16>), grid, 64, 0, s, part_out, seq_of_token,
+                  (__nv_bfloat16*)out, n_q, vd, num_splits);
+    return launch_status();
+}
+
 template <typename T, int NC>
 int launch_mixed_attention(const MixedAttentionArgs& a, int num_seqs, cudaStream_t s) {
     const size_t smem = (size_t)(MH_ROWS * a.d + MH_KEYS * (a.d + 1) + MH_KEYS * NC * 32 +
@@ -495,14 +507,7 @@ MB_EXPORT int mb_mixed_head_attention(const void* qkv, int row_width, const void
                                        : dispatch_mixed_attention<__nv_bfloat16>(a, num_seqs, s);
         if (rc != MB_OK) return rc;
     }
-    dim3 grid(tokens, n_q);
-    if (dtype == MB_F32)
-        MB_LAUNCH((mixed_head_sum_kernel<float>), grid, 64, 0, s, (const float*)a.part_out, seq_of_token,
-                  (float*)out, n_q, vd, num_splits);
-    else
-        MB_LAUNCH((mixed_head_sum_kernel<__nv_bfloat16>), grid, 64, 0, s, (const float*)a.part_out,
-                  seq_of_token, (__nv_bfloat16*)out, n_q, vd, num_splits);
-    return launch_status();
+    return launch_mixed_head_sum(a.part_out, seq_of_token, out, tokens, n_q, vd, num_splits, dtype, s);
 }
 
 MB_EXPORT int mb_rope_blend_store(void* qkv, const float* cos_t, const float* sin_t, int rot,

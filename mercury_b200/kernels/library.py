@@ -84,6 +84,10 @@ _SIGNATURES = {
                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_int,
                                 c_void_p, c_longlong, c_void_p],
+    "mb_mixed_head_attention_mma": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                    c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p,
+                                    c_longlong, c_void_p],
     "mb_rope_blend_store": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                             c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -135,6 +139,8 @@ def load():
     lib.mb_attention_decode_raw_pays.restype = c_int
     lib.mb_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mb_attention_scratch_floats.restype = c_longlong
+    lib.mb_mixed_head_mma_supports.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mb_mixed_head_mma_supports.restype = c_int
     lib.mb_mixed_head_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mb_mixed_head_scratch_floats.restype = c_longlong
     _LIB = lib

@@ -101,6 +101,8 @@ class CudaOps:
         # "auto": the tensor-memory (tcgen05) kernel for prompt portions of head sizes 64 and
         # 128, the mma.sync kernels for everything else; "mma": the mma.sync kernels only
         self.attention = "auto"
+        # the mixed-head attention: "auto" (tensor cores where they take the sizes) or "simt"
+        self.mixed_head = "auto"
         self.prompt_cluster: int | None = None  # override of the CTAs per row tile (1, 2, 4)
         # decode-like batches: the key ranges of a (sequence, KV head) as one cluster of up to
         # 8 blocks, merged through distributed shared memory, while fewer than 32 ranges are
@@ -590,15 +592,34 @@ class CudaOps:
         self.launches += 1
 
     @_timed("attention")
-    def mixed_head_attention(self, qkv, layout, batch, cache, scale, window, mix, out):
+    def mixed_head_attention(self, qkv, layout, batch, cache, scale, window, mix, out,
+                             kernel: str | None = None):
         """Attention over the pages whose heads' softmax weights are mixed by `mix`
-        [heads, heads] (float32, or None) before they meet the values."""
+        [heads, heads] (float32, or None) before they meet the values. bfloat16 with sizes
+        the tensor-core kernel takes runs there (`kernel` forces "mma" or "simt"), everything
+        else, and the float32 engine always, on the CUDA cores."""
         heads, kv_heads, dim, vdim = layout
         self._check_limits(cache)
         tokens = qkv.shape[0]
-        splits = self._mixed_head_splits(batch, heads)
+        mma_ok = (qkv.dtype == torch.bfloat16 and qkv.shape[1] % 8 == 0
+                  and bool(self.lib.mb_mixed_head_mma_supports(heads, kv_heads, dim, vdim)))
+        if kernel == "mma" and not mma_ok:
+            raise KernelError("the tensor-core mixed-head attention takes bfloat16, heads of a "
+                              "multiple of 16 features and value heads of a multiple of 8 up to 128")
+        use_mma = mma_ok and (kernel or self.mixed_head) != "simt"
+        splits = self._mixed_head_splits(batch, heads, 16 if use_mma else None)
         floats = self.lib.mb_mixed_head_scratch_floats(tokens, heads, vdim, splits)
         scratch = self._scratch_for(floats) if floats else None
+        if use_mma:
+            check(self.lib.mb_mixed_head_attention_mma(
+                _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
+                cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(mix), _ptr(out),
+                batch.num_seqs, batch.max_q_len, heads, kv_heads, dim, vdim, cache.page_size,
+                float(scale), int(window), splits, _ptr(batch.seq_of_token), tokens, _ptr(scratch),
+                scratch.numel() if scratch is not None else 0, self._stream()),
+                "mixed_head_attention (mma)")
+            self.launches += 1 if splits == 1 else 3
+            return
         check(self.lib.mb_mixed_head_attention(
             _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
             cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(mix), _ptr(out),
@@ -608,7 +629,7 @@ class CudaOps:
             "mixed_head_attention")
         self.launches += 1 if splits == 1 else 3
 
-    def _mixed_head_splits(self, batch, heads: int) -> int:
+    def _mixed_head_splits(self, batch, heads: int, rows: int | None = None) -> int:
         """Key ranges per row tile of the mixed-head attention: one block holds every head of
         a tile of tokens, so a decode step brings one block per sequence, and its keys are
         divided until the device is about filled. Inside a captured step (the batch names
@@ -616,7 +637,7 @@ class CudaOps:
         lengths; a block whose range is empty leaves zeros."""
         if self.decode_splits is not None:
             return max(1, self.decode_splits)
-        bq = max(1, min(64 // heads, 16, batch.max_q_len))
+        bq = rows or max(1, min(64 // heads, 16, batch.max_q_len))
         blocks = batch.num_seqs * -(-batch.max_q_len // bq)
         if blocks >= self.sm_count:
             return 1

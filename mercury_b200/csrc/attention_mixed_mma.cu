@@ -4,15 +4,18 @@
 //
 // A block takes 16 query tokens with all their heads and walks the keys twice in tiles of
 // 32, as the CUDA-core kernel does (first each row's maximum and sum, then the finished
-// weights). Head h belongs to warp h mod (number of warps). Per tile of the second walk:
+// weights). Head h belongs to warp h mod (number of warps). Key and value tiles come by
+// 16-byte cp.async copies into two buffers, the next tile under way while this one is used.
+// Per tile of the second walk:
 //   1. S_h = Q_h K^T on the tensor cores (bfloat16 operands are exact, float32 sums),
-//      w_h = exp(S_h * scale - max_h) / sum_h in float32 registers;
+//      w_h = 2^(S_h * scale * log2 e - max_h) / sum_h in float32 registers;
 //   2. every weight is split w = hi + lo into two bfloat16 numbers (|lo| <= 2^-9 |w|, what is
-//      left is below 2^-17 |w|) and written position-major, [token, key][head];
+//      left is below 2^-17 |w|) and written to shared memory as [head][token][key];
 //   3. the heads are mixed as a product over the head index, W' = M W: M (bfloat16 in the
-//      checkpoint, so exact) times hi and times lo, summed in float32; the result, split
-//      again, goes back head-major, [head][token][key];
-//   4. O_h += W'_h V on the tensor cores, hi and lo in turn, from a transposed value tile.
+//      checkpoint, so exact) times hi and times lo, summed in float32. A warp takes tiles
+//      of eight (token, key) places, reads every head's weights there (ldmatrix, transposed),
+//      and writes the mixed weights, split again, back to the same places;
+//   4. O_h += W'_h V on the tensor cores, hi and lo in turn, the value tile read transposed.
 // So the weights keep 16 bits of mantissa through both products, against the 8 that the
 // values they multiply have. The float32 engine never comes here.
 #include "common.cuh"
@@ -42,6 +45,8 @@ typedef __nv_bfloat16 bf;
 constexpr int MM_ROWS = 16;     // query tokens per block
 constexpr int MM_KEYS = 32;     // keys per tile
 constexpr int MM_PAD = 8;       // elements of padding per shared-memory row
+constexpr int MM_WROW = MM_KEYS + MM_PAD;              // a token's weights: 32 keys + padding
+constexpr int MM_WHEAD = MM_ROWS * MM_WROW + MM_PAD;   // a head's weights: 16 tokens + padding
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -53,6 +58,28 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 
 __device__ __forceinline__ uint32_t ld32(const bf* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
+// Two 8 x 8 tiles of 16-bit elements, transposed: the B operand (k = 16 rows of shared
+// memory, n = 8 columns) of one mma from row-major storage. Lanes 0-15 give the rows.
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* smem) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n"
+                 : "=r"(r0), "=r"(r1)
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void copy_16(void* smem, const void* gmem, bool valid) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zeroed
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(addr), "l"(gmem), "r"(bytes));
+}
+
+// 2^x by the special-function unit (relative error about 2^-22); 2^-inf = 0.
+__device__ __forceinline__ float exp2_fast(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& lo) {
     const bf xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
     const bf xl = __float2bfloat16_rn(x - __bfloat162float(xh));
@@ -62,7 +89,7 @@ __device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t&
 }
 
 struct MmaLayout {      // offsets in bytes of the shared-memory regions
-    int q, k, vt, p_hi, p_lo, m_hi, m_lo, t, pages, total;
+    int q, k, v, w_hi, w_lo, t, total;
 };
 
 __host__ __device__ inline MmaLayout mma_layout(int H, int G, int d, int vd) {
@@ -70,14 +97,11 @@ __host__ __device__ inline MmaLayout mma_layout(int H, int G, int d, int vd) {
     MmaLayout l;
     int at = 0;
     l.q = at;     at += H * MM_ROWS * (d + MM_PAD) * 2;
-    l.k = at;     at += G * MM_KEYS * (d + MM_PAD) * 2;
-    l.vt = at;    at += G * vd * (MM_KEYS + MM_PAD) * 2;
-    l.p_hi = at;  at += MM_ROWS * MM_KEYS * Hp * 2;
-    l.p_lo = at;  at += MM_ROWS * MM_KEYS * Hp * 2;
-    l.m_hi = at;  at += Hp * MM_ROWS * (MM_KEYS + MM_PAD) * 2;
-    l.m_lo = at;  at += Hp * MM_ROWS * (MM_KEYS + MM_PAD) * 2;
+    l.k = at;     at += 2 * G * MM_KEYS * (d + MM_PAD) * 2;       // two buffers
+    l.v = at;     at += 2 * G * MM_KEYS * (vd + MM_PAD) * 2;
+    l.w_hi = at;  at += Hp * MM_WHEAD * 2;
+    l.w_lo = at;  at += Hp * MM_WHEAD * 2;
     l.t = at;     at += Hp * Hp * 2;
-    l.pages = at; at += MM_KEYS * 4;
     l.total = at;
     return l;
 }
@@ -106,21 +130,20 @@ mixed_head_attention_mma_kernel(const MixedAttentionArgs a) {
     const MmaLayout L = mma_layout(H, G, d, vd);
     bf* q_s = reinterpret_cast<bf*>(smem_raw + L.q);
     bf* k_s = reinterpret_cast<bf*>(smem_raw + L.k);
-    bf* vt_s = reinterpret_cast<bf*>(smem_raw + L.vt);
-    bf* p_hi = reinterpret_cast<bf*>(smem_raw + L.p_hi);
-    bf* p_lo = reinterpret_cast<bf*>(smem_raw + L.p_lo);
-    bf* m_hi = reinterpret_cast<bf*>(smem_raw + L.m_hi);
-    bf* m_lo = reinterpret_cast<bf*>(smem_raw + L.m_lo);
+    bf* v_s = reinterpret_cast<bf*>(smem_raw + L.v);
+    bf* w_hi = reinterpret_cast<bf*>(smem_raw + L.w_hi);
+    bf* w_lo = reinterpret_cast<bf*>(smem_raw + L.w_lo);
     bf* t_s = reinterpret_cast<bf*>(smem_raw + L.t);
-    int* page_s = reinterpret_cast<int*>(smem_raw + L.pages);
-    const int qs = d + MM_PAD;                 // row strides in elements
-    const int ks = MM_KEYS + MM_PAD;
+    const int qs = d + MM_PAD, vs = vd + MM_PAD;       // row strides in elements
+    const int k_buf = G * MM_KEYS * qs, v_buf = G * MM_KEYS * vs;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
+    const int page_shift = __ffs(a.page_size) - 1;
 
-    // queries (zeros for rows beyond the tile), the mixing matrix (identity when absent)
-    const int chunks = d / 8;
+    // queries (zeros for rows beyond the tile), the mixing matrix (identity when absent),
+    // zeros in the weights of the heads that pad H to a multiple of 16
+    const int chunks = d / 8, vchunks = vd / 8;
     for (int idx = tid; idx < H * MM_ROWS * chunks; idx += NW * 32) {
         const int ch = idx % chunks, i = (idx / chunks) % MM_ROWS, h = idx / (chunks * MM_ROWS);
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -134,6 +157,10 @@ mixed_head_attention_mma_kernel(const MixedAttentionArgs a) {
         if (h < H && gg < H) v = a.mix ? a.mix[h * H + gg] : (h == gg ? 1.f : 0.f);
         t_s[idx] = __float2bfloat16_rn(v);
     }
+    for (int idx = tid; idx < (Hp - H) * MM_WHEAD; idx += NW * 32) {
+        w_hi[H * MM_WHEAD + idx] = __float2bfloat16_rn(0.f);
+        w_lo[H * MM_WHEAD + idx] = __float2bfloat16_rn(0.f);
+    }
 
     const int p_min = first_pos + tok0, p_max = first_pos + tok0 + n_tok - 1;
     int t_lo = 0;
@@ -145,9 +172,39 @@ mixed_head_attention_mma_kernel(const MixedAttentionArgs a) {
         if (t_lo + per < t_hi) t_hi = t_lo + per;
     }
 
+    // A tile's keys (and values) on their way into buffer `buf`; keys beyond the sequence
+    // and pages given back arrive as zeros.
+    auto issue = [&](int kt, int buf, bool with_values) {
+        for (int c = 0; c < G; ++c) {
+            for (int e = tid; e < MM_KEYS * chunks; e += NW * 32) {
+                const int j = e / chunks, ch = e - j * chunks;
+                const int key = kt * MM_KEYS + j;
+                int page = -1;
+                if (key < kv_len) page = table_page(a.table, seq, a.max_pages, key >> page_shift);
+                const bf* src = k_pages;
+                if (page >= 0)
+                    src += (((int64_t)page * G + c) * a.page_size + (key & (a.page_size - 1))) * d + ch * 8;
+                copy_16(k_s + buf * k_buf + (c * MM_KEYS + j) * qs + ch * 8, src, page >= 0);
+            }
+            if (!with_values) continue;
+            for (int e = tid; e < MM_KEYS * vchunks; e += NW * 32) {
+                const int j = e / vchunks, ch = e - j * vchunks;
+                const int key = kt * MM_KEYS + j;
+                int page = -1;
+                if (key < kv_len) page = table_page(a.table, seq, a.max_pages, key >> page_shift);
+                const bf* src = v_pages;
+                if (page >= 0)
+                    src += (((int64_t)page * G + c) * a.page_size + (key & (a.page_size - 1))) * vd + ch * 8;
+                copy_16(v_s + buf * v_buf + (c * MM_KEYS + j) * vs + ch * 8, src, page >= 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
     // rows of this thread: g and g + 8 of the tile
     const bool ok0 = g < n_tok, ok1 = g + 8 < n_tok;
     const int pos0 = first_pos + tok0 + g, pos1 = pos0 + 8;
+    const float to_log2 = a.scale * 1.4426950408889634f;     // scores in powers of two
 
     float row_m[HPW][2], row_l[HPW][2];
     float acc[HPW][NV][4];
@@ -175,7 +232,7 @@ mixed_head_attention_mma_kernel(const MixedAttentionArgs a) {
                 for (int z = 0; z < a.num_splits; ++z) big = fmaxf(big, ml[2 * z]);
                 float sum = 0.f;
                 for (int z = 0; z < a.num_splits; ++z)
-                    if (ml[2 * z] > -INFINITY) sum += ml[2 * z + 1] * expf(ml[2 * z] - big);
+                    if (ml[2 * z] > -INFINITY) sum += ml[2 * z + 1] * exp2_fast(ml[2 * z] - big);
                 row_m[hh][half] = big;
                 row_l[hh][half] = sum;
             }
@@ -191,43 +248,18 @@ mixed_head_attention_mma_kernel(const MixedAttentionArgs a) {
                 for (int half = 0; half < 2; ++half)
                     row_l[hh][half] = row_l[hh][half] > 0.f ? 1.f / row_l[hh][half] : 0.f;
         }
+        __syncthreads();       // the pass before is through with both buffers
+        if (t_lo < t_hi) issue(t_lo, 0, pass == 1);
         for (int kt = t_lo; kt < t_hi; ++kt) {
-            __syncthreads();
-            if (tid < MM_KEYS) {
-                const int key = kt * MM_KEYS + tid;
-                int page = -1;
-                if (key < kv_len) page = table_page(a.table, seq, a.max_pages, key / a.page_size);
-                page_s[tid] = page;
-            }
-            __syncthreads();
-            for (int idx = tid; idx < G * MM_KEYS * chunks; idx += NW * 32) {
-                const int ch = idx % chunks, j = (idx / chunks) % MM_KEYS, c = idx / (chunks * MM_KEYS);
-                const int page = page_s[j];
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (page >= 0) {
-                    const int key = kt * MM_KEYS + j;
-                    v = *reinterpret_cast<const uint4*>(
-                        k_pages + (((int64_t)page * G + c) * a.page_size + (key % a.page_size)) * d + ch * 8);
-                }
-                *reinterpret_cast<uint4*>(k_s + (c * MM_KEYS + j) * qs + ch * 8) = v;
-            }
-            if (pass == 1) {
-                const int vchunks = vd / 8;
-                for (int idx = tid; idx < G * MM_KEYS * vchunks; idx += NW * 32) {
-                    const int j = idx % MM_KEYS, ch = (idx / MM_KEYS) % vchunks, c = idx / (MM_KEYS * vchunks);
-                    const int page = page_s[j];
-                    uint4 v = make_uint4(0, 0, 0, 0);
-                    if (page >= 0) {
-                        const int key = kt * MM_KEYS + j;
-                        v = *reinterpret_cast<const uint4*>(
-                            v_pages + (((int64_t)page * G + c) * a.page_size + (key % a.page_size)) * vd + ch * 8);
-                    }
-                    const bf* e = reinterpret_cast<const bf*>(&v);
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) vt_s[(c * vd + ch * 8 + x) * ks + j] = e[x];
-                }
-            }
-            __syncthreads();
+            const int buf = (kt - t_lo) & 1;
+            asm volatile("cp.async.wait_group 0;\n" ::);
+            __syncthreads();   // this tile has arrived for everyone; the tile before is consumed
+            if (kt + 1 < t_hi) issue(kt + 1, buf ^ 1, pass == 1);
+            const bf* kb = k_s + buf * k_buf;
+            const bf* vb = v_s + buf * v_buf;
+            // a tile that every row sees whole needs no mask
+            const bool whole = kt * MM_KEYS + MM_KEYS - 1 <= p_min && n_tok == MM_ROWS &&
+                               (a.window <= 0 || kt * MM_KEYS > p_max - a.window);
 
             // 1. scores and weights of this warp's heads
 #pragma unroll
@@ -241,6 +273,7 @@ mixed_head_attention_mma_kernel(const MixedAttentionArgs a) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
                 const bf* qrow = q_s + (h * MM_ROWS + g) * qs + 2 * t;
+                const bf* krow = kb + (c * MM_KEYS + g) * qs + 2 * t;
                 for (int k0 = 0; k0 < d; k0 += 16) {
                     uint32_t af[4];
                     af[0] = ld32(qrow + k0);
@@ -248,106 +281,111 @@ mixed_head_attention_mma_kernel(const MixedAttentionArgs a) {
                     af[2] = ld32(qrow + k0 + 8);
                     af[3] = ld32(qrow + 8 * qs + k0 + 8);
 #pragma unroll
-                    for (int nt = 0; nt < 4; ++nt) {
-                        const bf* krow = k_s + (c * MM_KEYS + nt * 8 + g) * qs + k0 + 2 * t;
-                        mma_16816(s[nt], af, ld32(krow), ld32(krow + 8));
-                    }
+                    for (int nt = 0; nt < 4; ++nt)
+                        mma_16816(s[nt], af, ld32(krow + nt * 8 * qs + k0), ld32(krow + nt * 8 * qs + k0 + 8));
                 }
-                // what each element may see
-                float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int j = nt * 8 + 2 * t + (e & 1);
-                        const int key = kt * MM_KEYS + j;
-                        const bool second = e >= 2;
-                        const int pos = second ? pos1 : pos0;
-                        bool seen = (second ? ok1 : ok0) && page_s[j] >= 0 && key <= pos;
-                        if (a.window > 0) seen = seen && key > pos - a.window;
-                        s[nt][e] = seen ? s[nt][e] * a.scale : -INFINITY;
-                        if (second) mx1 = fmaxf(mx1, s[nt][e]); else mx0 = fmaxf(mx0, s[nt][e]);
-                    }
+                    for (int e = 0; e < 4; ++e) s[nt][e] *= to_log2;
+                if (!whole) {
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int key = kt * MM_KEYS + nt * 8 + 2 * t + (e & 1);
+                            const int pos = e >= 2 ? pos1 : pos0;
+                            bool seen = (e >= 2 ? ok1 : ok0) && key <= pos;
+                            if (a.window > 0) seen = seen && key > pos - a.window;
+                            if (!seen) s[nt][e] = -INFINITY;
+                        }
+                }
                 if (pass == 0) {
+                    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+                        mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+                    }
                     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
                     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
                     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
                     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
                     const float n0 = fmaxf(row_m[hh][0], mx0), n1 = fmaxf(row_m[hh][1], mx1);
+                    // a row that has seen nothing yet keeps its maximum at -inf and adds zeros
+                    const float b0 = n0 > -INFINITY ? n0 : 0.f, b1 = n1 > -INFINITY ? n1 : 0.f;
                     float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
                     for (int nt = 0; nt < 4; ++nt) {
-                        if (n0 > -INFINITY) sum0 += (s[nt][0] > -INFINITY ? expf(s[nt][0] - n0) : 0.f) +
-                                                    (s[nt][1] > -INFINITY ? expf(s[nt][1] - n0) : 0.f);
-                        if (n1 > -INFINITY) sum1 += (s[nt][2] > -INFINITY ? expf(s[nt][2] - n1) : 0.f) +
-                                                    (s[nt][3] > -INFINITY ? expf(s[nt][3] - n1) : 0.f);
+                        sum0 += exp2_fast(s[nt][0] - b0) + exp2_fast(s[nt][1] - b0);
+                        sum1 += exp2_fast(s[nt][2] - b1) + exp2_fast(s[nt][3] - b1);
                     }
                     sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
                     sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
                     sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
                     sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
-                    const float c0 = n0 > -INFINITY ? expf(row_m[hh][0] - n0) : 1.f;
-                    const float c1 = n1 > -INFINITY ? expf(row_m[hh][1] - n1) : 1.f;
-                    row_l[hh][0] = row_l[hh][0] * c0 + sum0;
-                    row_l[hh][1] = row_l[hh][1] * c1 + sum1;
+                    row_l[hh][0] = row_l[hh][0] * exp2_fast(row_m[hh][0] - b0) + sum0;
+                    row_l[hh][1] = row_l[hh][1] * exp2_fast(row_m[hh][1] - b1) + sum1;
                     row_m[hh][0] = n0;
                     row_m[hh][1] = n1;
                     continue;
                 }
-                // 2. finished weights, split, position-major
+                // 2. finished weights, split, [head][token][key]
+                const float m0 = row_m[hh][0] > -INFINITY ? row_m[hh][0] : 0.f;
+                const float m1 = row_m[hh][1] > -INFINITY ? row_m[hh][1] : 0.f;
+                bf* wh = w_hi + h * MM_WHEAD + g * MM_WROW + 2 * t;
+                bf* wl = w_lo + h * MM_WHEAD + g * MM_WROW + 2 * t;
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int half = e >> 1;
-                        float p = 0.f;
-                        if (s[nt][e] > -INFINITY) p = expf(s[nt][e] - row_m[hh][half]) * row_l[hh][half];
-                        const bf ph = __float2bfloat16_rn(p);
-                        const bf pl = __float2bfloat16_rn(p - __bfloat162float(ph));
-                        const int at = ((g + 8 * half) * MM_KEYS + nt * 8 + 2 * t + (e & 1)) * Hp + h;
-                        p_hi[at] = ph;
-                        p_lo[at] = pl;
-                    }
+                for (int nt = 0; nt < 4; ++nt) {
+                    uint32_t hi, lo;
+                    split2(exp2_fast(s[nt][0] - m0) * row_l[hh][0], exp2_fast(s[nt][1] - m0) * row_l[hh][0], hi, lo);
+                    *reinterpret_cast<uint32_t*>(wh + nt * 8) = hi;
+                    *reinterpret_cast<uint32_t*>(wl + nt * 8) = lo;
+                    split2(exp2_fast(s[nt][2] - m1) * row_l[hh][1], exp2_fast(s[nt][3] - m1) * row_l[hh][1], hi, lo);
+                    *reinterpret_cast<uint32_t*>(wh + 8 * MM_WROW + nt * 8) = hi;
+                    *reinterpret_cast<uint32_t*>(wl + 8 * MM_WROW + nt * 8) = lo;
+                }
             }
             if (pass == 0) continue;
-            // heads beyond H never write: their columns must read as zero
-            if (Hp > H)
-                for (int idx = tid; idx < MM_ROWS * MM_KEYS * (Hp - H); idx += NW * 32) {
-                    const int at = (idx / (Hp - H)) * Hp + H + idx % (Hp - H);
-                    p_hi[at] = __float2bfloat16_rn(0.f);
-                    p_lo[at] = __float2bfloat16_rn(0.f);
-                }
             __syncthreads();
 
-            // 3. the heads mixed: W'[h][pos] = sum_g M[h][g] W[g][pos]
-            for (int ntile = warp; ntile < MM_ROWS * MM_KEYS / 8; ntile += NW) {
-                const int pos_b = ntile * 8 + g;          // B operand: column n = g
-                for (int mt = 0; mt < Hp / 16; ++mt) {
+            // 3. the heads mixed, in place: a warp owns tiles of eight places (token i, keys
+            // 8 jb .. 8 jb + 7), reads every head's weights there and writes the mixed ones back
+            for (int place = warp; place < MM_ROWS * MM_KEYS / 8; place += NW) {
+                const int i = place >> 2, jb = place & 3;
+                const int at = i * MM_WROW + jb * 8;
+                uint32_t bh[2][2], bl[2][2];
+#pragma unroll
+                for (int kk = 0; kk < 2; ++kk) {
+                    if (kk * 16 >= Hp) break;
+                    const int head = kk * 16 + (lane & 15);
+                    ldmatrix_x2_trans(bh[kk][0], bh[kk][1], w_hi + head * MM_WHEAD + at);
+                    ldmatrix_x2_trans(bl[kk][0], bl[kk][1], w_lo + head * MM_WHEAD + at);
+                }
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    if (mt * 16 >= Hp) break;
                     float cm[4] = {0.f, 0.f, 0.f, 0.f};
-                    for (int kk = 0; kk < Hp / 16; ++kk) {
+#pragma unroll
+                    for (int kk = 0; kk < 2; ++kk) {
+                        if (kk * 16 >= Hp) break;
                         uint32_t af[4];
                         const bf* trow = t_s + (mt * 16 + g) * Hp + kk * 16 + 2 * t;
                         af[0] = ld32(trow);
                         af[1] = ld32(trow + 8 * Hp);
                         af[2] = ld32(trow + 8);
                         af[3] = ld32(trow + 8 * Hp + 8);
-                        const bf* ph = p_hi + pos_b * Hp + kk * 16 + 2 * t;
-                        const bf* pl = p_lo + pos_b * Hp + kk * 16 + 2 * t;
-                        mma_16816(cm, af, ld32(ph), ld32(ph + 8));
-                        mma_16816(cm, af, ld32(pl), ld32(pl + 8));
+                        mma_16816(cm, af, bh[kk][0], bh[kk][1]);
+                        mma_16816(cm, af, bl[kk][0], bl[kk][1]);
                     }
-                    // C: rows h = mt * 16 + g (+ 8), columns pos = ntile * 8 + 2t, + 1
-                    const int pos_c = ntile * 8 + 2 * t;
-                    const int i = pos_c / MM_KEYS, j = pos_c % MM_KEYS;
+                    // C: rows = heads mt * 16 + g (+ 8), columns = keys 8 jb + 2t, + 1
                     uint32_t hi, lo;
                     split2(cm[0], cm[1], hi, lo);
-                    const int at0 = ((mt * 16 + g) * MM_ROWS + i) * ks + j;
-                    *reinterpret_cast<uint32_t*>(m_hi + at0) = hi;
-                    *reinterpret_cast<uint32_t*>(m_lo + at0) = lo;
+                    *reinterpret_cast<uint32_t*>(w_hi + (mt * 16 + g) * MM_WHEAD + at + 2 * t) = hi;
+                    *reinterpret_cast<uint32_t*>(w_lo + (mt * 16 + g) * MM_WHEAD + at + 2 * t) = lo;
                     split2(cm[2], cm[3], hi, lo);
-                    const int at1 = ((mt * 16 + g + 8) * MM_ROWS + i) * ks + j;
-                    *reinterpret_cast<uint32_t*>(m_hi + at1) = hi;
-                    *reinterpret_cast<uint32_t*>(m_lo + at1) = lo;
+                    *reinterpret_cast<uint32_t*>(w_hi + (mt * 16 + g + 8) * MM_WHEAD + at + 2 * t) = hi;
+                    *reinterpret_cast<uint32_t*>(w_lo + (mt * 16 + g + 8) * MM_WHEAD + at + 2 * t) = lo;
                 }
             }
             __syncthreads();
@@ -361,15 +399,16 @@ mixed_head_attention_mma_kernel(const MixedAttentionArgs a) {
 #pragma unroll
                 for (int k0 = 0; k0 < MM_KEYS; k0 += 16) {
                     uint32_t ah[4], al[4];
-                    const bf* mh = m_hi + (h * MM_ROWS + g) * ks + k0 + 2 * t;
-                    const bf* ml = m_lo + (h * MM_ROWS + g) * ks + k0 + 2 * t;
-                    ah[0] = ld32(mh); ah[1] = ld32(mh + 8 * ks); ah[2] = ld32(mh + 8); ah[3] = ld32(mh + 8 * ks + 8);
-                    al[0] = ld32(ml); al[1] = ld32(ml + 8 * ks); al[2] = ld32(ml + 8); al[3] = ld32(ml + 8 * ks + 8);
+                    const bf* mh = w_hi + h * MM_WHEAD + g * MM_WROW + k0 + 2 * t;
+                    const bf* ml = w_lo + h * MM_WHEAD + g * MM_WROW + k0 + 2 * t;
+                    ah[0] = ld32(mh); ah[1] = ld32(mh + 8 * MM_WROW); ah[2] = ld32(mh + 8); ah[3] = ld32(mh + 8 * MM_WROW + 8);
+                    al[0] = ld32(ml); al[1] = ld32(ml + 8 * MM_WROW); al[2] = ld32(ml + 8); al[3] = ld32(ml + 8 * MM_WROW + 8);
+                    const bf* vrow = vb + (c * MM_KEYS + k0 + (lane & 15)) * vs;
 #pragma unroll
                     for (int n = 0; n < NV; ++n) {
                         if (n * 8 >= vd) break;
-                        const bf* vrow = vt_s + (c * vd + n * 8 + g) * ks + k0 + 2 * t;
-                        const uint32_t b0 = ld32(vrow), b1 = ld32(vrow + 8);
+                        uint32_t b0, b1;
+                        ldmatrix_x2_trans(b0, b1, vrow + n * 8);
                         mma_16816(acc[hh][n], ah, b0, b1);
                         mma_16816(acc[hh][n], al, b0, b1);
                     }

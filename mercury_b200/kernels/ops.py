@@ -103,6 +103,8 @@ class CudaOps:
         self.attention = "auto"
         # the mixed-head attention: "auto" (tensor cores where they take the sizes) or "simt"
         self.mixed_head = "auto"
+        self.mixed_head_blocks_per_sm = 8
+        self.mixed_head_max_splits = 32
         self.prompt_cluster: int | None = None  # override of the CTAs per row tile (1, 2, 4)
         # decode-like batches: the key ranges of a (sequence, KV head) as one cluster of up to
         # 8 blocks, merged through distributed shared memory, while fewer than 32 ranges are
@@ -630,22 +632,25 @@ class CudaOps:
         self.launches += 1 if splits == 1 else 3
 
     def _mixed_head_splits(self, batch, heads: int, rows: int | None = None) -> int:
-        """Key ranges per row tile of the mixed-head attention: one block holds every head of
-        a tile of tokens, so a decode step brings one block per sequence, and its keys are
-        divided until the device is about filled. Inside a captured step (the batch names
-        `attention_splits`) the count depends on the batch's shape only, never on its
-        lengths; a block whose range is empty leaves zeros."""
+        """Key ranges per row tile of the mixed-head attention. One block holds every head of
+        a tile of tokens, so a step brings few blocks (one per sequence when decoding, 128
+        for a 2048-token prompt on the tensor-core kernel) and the longest of them walks
+        every key twice: the keys are divided until the device holds about
+        `mixed_head_blocks_per_sm` blocks per SM, at most `mixed_head_max_splits` ways.
+        Inside a captured step (the batch names `attention_splits`) the count depends on the
+        batch's shape only, never on its lengths; a block whose range is empty leaves zeros.
+        `rows`: tokens per block of the tensor-core kernel (the CUDA-core kernel's follow
+        from the head count)."""
         if self.decode_splits is not None:
             return max(1, self.decode_splits)
         bq = rows or max(1, min(64 // heads, 16, batch.max_q_len))
         blocks = batch.num_seqs * -(-batch.max_q_len // bq)
-        if blocks >= self.sm_count:
-            return 1
-        fill = min(64, -(-2 * self.sm_count // blocks))
+        fill = max(1, min(self.mixed_head_max_splits,
+                          self.mixed_head_blocks_per_sm * self.sm_count // blocks))
         if getattr(batch, "attention_splits", None):
             return fill
         key_tiles = -(-batch.max_kv_len // 32)
-        return max(1, min(fill, key_tiles // 4))
+        return max(1, min(fill, key_tiles // 2))
 
     def qkv_rope_store(self, x, weight, bias, qkv, num_heads, num_kv_heads, head_dim, tables,
                        batch, cache):

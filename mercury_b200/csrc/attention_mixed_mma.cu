@@ -80,12 +80,14 @@ __device__ __forceinline__ float exp2_fast(float x) {
     return y;
 }
 
+// (x, y) as two pairs of bfloat16: hi = the nearest bfloat16 numbers, lo = what they miss,
+// rounded again. One packed conversion per pair; a bfloat16 widens to float32 by a shift.
 __device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& lo) {
-    const bf xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
-    const bf xl = __float2bfloat16_rn(x - __bfloat162float(xh));
-    const bf yl = __float2bfloat16_rn(y - __bfloat162float(yh));
-    hi = (uint32_t)__bfloat16_as_ushort(xh) | ((uint32_t)__bfloat16_as_ushort(yh) << 16);
-    lo = (uint32_t)__bfloat16_as_ushort(xl) | ((uint32_t)__bfloat16_as_ushort(yl) << 16);
+    const __nv_bfloat162 h2 = __floats2bfloat162_rn(x, y);
+    hi = *reinterpret_cast<const uint32_t*>(&h2);
+    const float xh = __uint_as_float(hi << 16), yh = __uint_as_float(hi & 0xffff0000u);
+    const __nv_bfloat162 l2 = __floats2bfloat162_rn(x - xh, y - yh);
+    lo = *reinterpret_cast<const uint32_t*>(&l2);
 }
 
 struct MmaLayout {      // offsets in bytes of the shared-memory regions
@@ -514,9 +516,11 @@ MB_EXPORT int mb_mixed_head_attention_mma(const void* qkv, int row_width, const 
     const int nv = vd / 8;
     auto run = [&](const MixedAttentionArgs& args) -> int {
 #define MB_MM_CASE(NWV, HPWV, NVV) return launch_mixed_mma<NWV, HPWV, NVV>(args, num_seqs, s)
+        // a warp per head while there are at most 16 heads (more warps hide more latency
+        // than fewer warps with two heads each), two heads per warp beyond
         if (vd <= 64) {
             if (n_q <= 8) { if (nv <= 4) MB_MM_CASE(8, 1, 4); MB_MM_CASE(8, 1, 8); }
-            if (n_q <= 16) { if (nv <= 4) MB_MM_CASE(8, 2, 4); MB_MM_CASE(8, 2, 8); }
+            if (n_q <= 16) { if (nv <= 4) MB_MM_CASE(16, 1, 4); MB_MM_CASE(16, 1, 8); }
             if (nv <= 4) MB_MM_CASE(16, 2, 4);
             MB_MM_CASE(16, 2, 8);
         }

@@ -17,8 +17,9 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 
 // ---- the scan ----------------------------------------------------------------------------
 // Both recurrences are S_t = a_t S_{t-1} + b_t per channel, with a_t, b_t read off the
-// token alone. A block takes 32 channels of one sequence and cuts the step's tokens into
-// blockDim.y runs: every thread first folds its run into (A, B) with S_end = A S_start + B,
+// token alone. A block takes blockDim.x channels of one sequence (8 when the step is cut
+// into runs, so that a long prompt spreads over many SMs; 32 for a decode step) and cuts the
+// step's tokens into blockDim.y runs: every thread first folds its run into (A, B) with S_end = A S_start + B,
 // one thread per channel chains the runs' starts, and every thread then walks its run again
 // from its start and writes the outputs. The state that goes on to the next step is the
 // last run's own final value. A decode step (one token) is a single run.
@@ -90,7 +91,7 @@ mingru_scan_kernel(const float* __restrict__ pre, float* __restrict__ state,
                    const int* __restrict__ q_start, const int* __restrict__ slots,
                    T* __restrict__ out, int width) {
     grid_dependency_sync();
-    const int c = blockIdx.x * SC_CHANNELS + threadIdx.x;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int seq = blockIdx.y;
     const int begin = q_start[seq], end = q_start[seq + 1];
     if (begin >= end) return;
@@ -127,44 +128,60 @@ __global__ void causal_conv_kernel(const float* __restrict__ pre, int ld, int of
 }
 
 // gates[t][kind * width + b * size + o] = sigmoid(sum_i w[kind][b][i][o] * u[t][b * size + i]
-// + bias[kind][b][o]): block-diagonal products in float32, the weights held input-major so
-// that consecutive threads (outputs o) read consecutive addresses. A block computes 128
-// outputs of one (kind, block b) for 16 tokens; i ascends, so the sum's order is fixed.
-constexpr int BG_TOKENS = 16;
-
+// + bias[kind][b][o]) for the two kinds of gate (r, i): block-diagonal products in float32
+// FMAs, the weights held input-major so that consecutive threads (outputs o) read
+// consecutive addresses. A block computes 128 outputs of one block b, both kinds (they read
+// the same inputs), for BG_TOKENS tokens (32 in a prompt step, 8 in a decode step), the inputs
+// staged token-minor so that four tokens come with one shared-memory load; i ascends, so the
+// order of each sum is fixed.
+template <int BG_TOKENS>
 __global__ void __launch_bounds__(128)
 block_gates_kernel(const float* __restrict__ u, const float* __restrict__ w,
                    const float* __restrict__ bias, float* __restrict__ gates, int tokens, int width,
-                   int blocks, int size, int kinds) {
+                   int blocks, int size) {
     grid_dependency_sync();
-    extern __shared__ float u_s[];          // [BG_TOKENS][size]
-    const int per = (size + 127) / 128;     // output tiles per (kind, block)
+    extern __shared__ __align__(16) float u_s[];          // [size][BG_TOKENS]
+    const int per = (size + 127) / 128;                  // output tiles per block b
     const int otile = blockIdx.x % per;
-    const int b = (blockIdx.x / per) % blocks;
-    const int kind = blockIdx.x / (per * blocks);
+    const int b = blockIdx.x / per;
     const int t0 = blockIdx.y * BG_TOKENS;
     for (int idx = threadIdx.x; idx < BG_TOKENS * size; idx += blockDim.x) {
         const int tt = idx / size, i = idx - tt * size;
-        u_s[idx] = t0 + tt < tokens ? u[(int64_t)(t0 + tt) * width + b * size + i] : 0.f;
+        u_s[i * BG_TOKENS + tt] = t0 + tt < tokens ? u[(int64_t)(t0 + tt) * width + b * size + i] : 0.f;
     }
     __syncthreads();
     const int o = otile * 128 + threadIdx.x;
     if (o >= size) return;
-    const float* wp = w + ((int64_t)(kind * blocks + b) * size) * size + o;
-    float acc[BG_TOKENS];
+    const float* wr = w + ((int64_t)b * size) * size + o;                    // kind 0
+    const float* wi = w + ((int64_t)(blocks + b) * size) * size + o;         // kind 1
+    float ar[BG_TOKENS], ai[BG_TOKENS];
 #pragma unroll
-    for (int tt = 0; tt < BG_TOKENS; ++tt) acc[tt] = 0.f;
+    for (int tt = 0; tt < BG_TOKENS; ++tt) ar[tt] = ai[tt] = 0.f;
+#pragma unroll 4
     for (int i = 0; i < size; ++i) {
-        const float wv = wp[(int64_t)i * size];
+        const float vr = wr[(int64_t)i * size], vi = wi[(int64_t)i * size];
+        const float4* row = reinterpret_cast<const float4*>(u_s + i * BG_TOKENS);
 #pragma unroll
-        for (int tt = 0; tt < BG_TOKENS; ++tt) acc[tt] = fmaf(wv, u_s[tt * size + i], acc[tt]);
+        for (int q = 0; q < BG_TOKENS / 4; ++q) {
+            const float4 x = row[q];
+            ar[4 * q] = fmaf(vr, x.x, ar[4 * q]);
+            ar[4 * q + 1] = fmaf(vr, x.y, ar[4 * q + 1]);
+            ar[4 * q + 2] = fmaf(vr, x.z, ar[4 * q + 2]);
+            ar[4 * q + 3] = fmaf(vr, x.w, ar[4 * q + 3]);
+            ai[4 * q] = fmaf(vi, x.x, ai[4 * q]);
+            ai[4 * q + 1] = fmaf(vi, x.y, ai[4 * q + 1]);
+            ai[4 * q + 2] = fmaf(vi, x.z, ai[4 * q + 2]);
+            ai[4 * q + 3] = fmaf(vi, x.w, ai[4 * q + 3]);
+        }
     }
-    const float bv = bias[(kind * blocks + b) * size + o];
+    const float br = bias[b * size + o], bi = bias[(blocks + b) * size + o];
 #pragma unroll
     for (int tt = 0; tt < BG_TOKENS; ++tt)
-        if (t0 + tt < tokens)
-            gates[(int64_t)(t0 + tt) * kinds * width + kind * width + b * size + o] =
-                sigmoid_f(acc[tt] + bv);
+        if (t0 + tt < tokens) {
+            float* row = gates + (int64_t)(t0 + tt) * 2 * width + b * size + o;
+            row[0] = sigmoid_f(ar[tt] + br);
+            row[width] = sigmoid_f(ai[tt] + bi);
+        }
 }
 
 // pre: [tokens][2 * width] float32 = [branch y | convolution input x]; u: the convolution's
@@ -196,7 +213,7 @@ gated_recurrence_scan_kernel(const float* __restrict__ pre, const float* __restr
                              const int* __restrict__ q_start, const int* __restrict__ slots,
                              T* __restrict__ out, int width, int taps) {
     grid_dependency_sync();
-    const int c = blockIdx.x * SC_CHANNELS + threadIdx.x;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int seq = blockIdx.y;
     const int begin = q_start[seq], end = q_start[seq + 1];
     if (begin >= end) return;
@@ -232,8 +249,10 @@ MB_EXPORT int mb_mingru_scan(const float* pre, float* state, const int* q_start,
                              void* stream) {
     if (num_seqs <= 0 || width <= 0) return MB_OK;
     if (num_seqs > 65535) return MB_ERR_UNSUPPORTED_SIZE;
-    dim3 grid((width + SC_CHANNELS - 1) / SC_CHANNELS, num_seqs);
-    dim3 block(SC_CHANNELS, scan_run_count(max_q_len));
+    const int runs = scan_run_count(max_q_len);
+    const int channels = runs > 1 ? 8 : SC_CHANNELS;
+    dim3 grid((width + channels - 1) / channels, num_seqs);
+    dim3 block(channels, runs);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MB_F32)
         MB_LAUNCH((mingru_scan_kernel<float>), grid, block, 0, s, pre, state, q_start, slots, (float*)out, width);
@@ -261,22 +280,29 @@ MB_EXPORT int mb_causal_conv(const float* pre, int ld, int offset, const float* 
 MB_EXPORT int mb_block_gates(const float* u, const float* w, const float* bias, float* gates,
                              int tokens, int width, int blocks, int kinds, void* stream) {
     if (tokens <= 0 || width <= 0) return MB_OK;
-    if (blocks <= 0 || width % blocks) return MB_ERR_UNSUPPORTED_SIZE;
+    if (blocks <= 0 || width % blocks || kinds != 2) return MB_ERR_UNSUPPORTED_SIZE;
     const int size = width / blocks;
-    const size_t smem = (size_t)BG_TOKENS * size * sizeof(float);
+    const int tile = tokens <= 16 ? 8 : 32;
+    const size_t smem = (size_t)tile * size * sizeof(float);
     if (smem > 200 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
-    static size_t raised = 0;
-    if (smem > 48 * 1024 && smem > raised) {
-        if (cudaFuncSetAttribute(block_gates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem) != cudaSuccess)
-            return MB_ERR_UNSUPPORTED_SIZE;
-        raised = smem;
+    static size_t raised[2] = {0, 0};
+    size_t& mine = raised[tile == 8 ? 0 : 1];
+    if (smem > 48 * 1024 && smem > mine) {
+        const cudaError_t rc = tile == 8
+            ? cudaFuncSetAttribute(block_gates_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+            : cudaFuncSetAttribute(block_gates_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (rc != cudaSuccess) return MB_ERR_UNSUPPORTED_SIZE;
+        mine = smem;
     }
-    const int rows = (tokens + BG_TOKENS - 1) / BG_TOKENS;
+    const int rows = (tokens + tile - 1) / tile;
     if (rows > 65535) return MB_ERR_UNSUPPORTED_SIZE;
-    dim3 grid(((size + 127) / 128) * blocks * kinds, rows);
-    MB_LAUNCH((block_gates_kernel), grid, 128, smem, (cudaStream_t)stream, u, w, bias, gates, tokens,
-              width, blocks, size, kinds);
+    dim3 grid(((size + 127) / 128) * blocks, rows);
+    if (tile == 8)
+        MB_LAUNCH((block_gates_kernel<8>), grid, 128, smem, (cudaStream_t)stream, u, w, bias, gates,
+                  tokens, width, blocks, size);
+    else
+        MB_LAUNCH((block_gates_kernel<32>), grid, 128, smem, (cudaStream_t)stream, u, w, bias, gates,
+                  tokens, width, blocks, size);
     return launch_status();
 }
 
@@ -287,8 +313,10 @@ MB_EXPORT int mb_gated_recurrence_scan(const float* pre, const float* u, const f
                                        void* stream) {
     if (num_seqs <= 0 || width <= 0) return MB_OK;
     if (taps < 1 || taps > 16 || num_seqs > 65535) return MB_ERR_UNSUPPORTED_SIZE;
-    dim3 grid((width + SC_CHANNELS - 1) / SC_CHANNELS, num_seqs);
-    dim3 block(SC_CHANNELS, scan_run_count(max_q_len));
+    const int runs = scan_run_count(max_q_len);
+    const int channels = runs > 1 ? 8 : SC_CHANNELS;
+    dim3 grid((width + channels - 1) / channels, num_seqs);
+    dim3 block(channels, runs);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MB_F32)
         MB_LAUNCH((gated_recurrence_scan_kernel<float>), grid, block, 0, s, pre, u, gates, softplus_lam,

@@ -103,7 +103,7 @@ class CudaOps:
         self.attention = "auto"
         # the mixed-head attention: "auto" (tensor cores where they take the sizes) or "simt"
         self.mixed_head = "auto"
-        self.mixed_head_blocks_per_sm = 8
+        self.mixed_head_blocks_per_sm = 4
         self.mixed_head_max_splits = 32
         self.prompt_cluster: int | None = None  # override of the CTAs per row tile (1, 2, 4)
         # decode-like batches: the key ranges of a (sequence, KV head) as one cluster of up to
@@ -155,6 +155,7 @@ class CudaOps:
         self._tc_error: torch.Tensor | None = None   # error word of the tcgen05 kernels
         self._tc_pending = False
         self._argmax_scratch: torch.Tensor | None = None
+        self._float_biases: dict = {}
         self._timing: list | None = None      # (kind, start event, stop event) while timing
         self._timing_depth = 0
         self._event_overhead_ms: float | None = None
@@ -459,8 +460,17 @@ class CudaOps:
         else:
             torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
             if bias is not None:
-                out.add_(bias.float())
+                out.add_(self._float_bias(bias))
         self.library_calls += 1
+
+    def _float_bias(self, bias):
+        """The float32 copy of a bias, made once per tensor (a product whose result stays
+        float32 adds its bias in float32)."""
+        key = bias.data_ptr()
+        held = self._float_biases.get(key)
+        if held is None or held[0] is not bias:
+            held = self._float_biases[key] = (bias, bias.float())
+        return held[1]
 
     @_timed("gated product")
     def linear_swiglu(self, x, weight, out, ctx, ahead=None):

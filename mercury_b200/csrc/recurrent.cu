@@ -19,12 +19,12 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 // Both recurrences are S_t = a_t S_{t-1} + b_t per channel, with a_t, b_t read off the
 // token alone. A block takes blockDim.x channels of one sequence (8 when the step is cut
 // into runs, so that a long prompt spreads over many SMs; 32 for a decode step) and cuts the
-// step's tokens into blockDim.y runs: every thread first folds its run into (A, B) with S_end = A S_start + B,
+// step's tokens into blockDim.y runs (up to 64): every thread first folds its run into (A, B) with S_end = A S_start + B,
 // one thread per channel chains the runs' starts, and every thread then walks its run again
 // from its start and writes the outputs. The state that goes on to the next step is the
 // last run's own final value. A decode step (one token) is a single run.
 constexpr int SC_CHANNELS = 32;
-constexpr int SC_MAX_RUNS = 32;
+constexpr int SC_MAX_RUNS = 64;
 
 template <typename T, typename F>
 __device__ __forceinline__ void scan_runs(const F& f, float* cell, int begin, int end, int c,
@@ -36,13 +36,15 @@ __device__ __forceinline__ void scan_runs(const F& f, float* cell, int begin, in
     const int t0 = min(end, begin + k * len), t1 = min(end, t0 + len);
     if (runs > 1) {
         float A = 1.f, B = 0.f;
-        if (live)
+        if (live) {
+#pragma unroll 4
             for (int t = t0; t < t1; ++t) {
                 float a, b, o;
-                f(t, c, a, b, o);
+                f(t, c, a, b, o, false);      // the output's gate is not needed for the fold
                 B = a * B + b;
                 A *= a;
             }
+        }
         run_a[k][x] = A;
         run_b[k][x] = B;
         __syncthreads();
@@ -61,7 +63,7 @@ __device__ __forceinline__ void scan_runs(const F& f, float* cell, int begin, in
 #pragma unroll 4
     for (int t = t0; t < t1; ++t) {
         float a, b, o;
-        f(t, c, a, b, o);
+        f(t, c, a, b, o, true);
         s = a * s + b;
         out[(int64_t)t * width + c] = from_float<T>(s * o);
     }
@@ -74,19 +76,24 @@ __device__ __forceinline__ void scan_runs(const F& f, float* cell, int begin, in
 struct MinGruStep {
     const float* pre;
     int width;
-    __device__ __forceinline__ void operator()(int t, int c, float& a, float& b, float& o) const {
+    __device__ __forceinline__ void operator()(int t, int c, float& a, float& b, float& o,
+                                               bool with_gate) const {
+        // read-only loads: they may move ahead of the stores of the tokens before
         const float* row = pre + (int64_t)t * 3 * width;
-        const float z = sigmoid_f(row[c]);
-        const float u = row[width + c];
-        const float g = row[2 * width + c];
+        const float z = sigmoid_f(__ldg(row + c));
+        const float u = __ldg(row + width + c);
         a = 1.f - z;
         b = z * (u >= 0.f ? u + 0.5f : sigmoid_f(u));
-        o = g * sigmoid_f(g);
+        o = 0.f;
+        if (with_gate) {
+            const float g = __ldg(row + 2 * width + c);
+            o = g * sigmoid_f(g);
+        }
     }
 };
 
 template <typename T>
-__global__ void __launch_bounds__(SC_CHANNELS * SC_MAX_RUNS)
+__global__ void __launch_bounds__(1024)
 mingru_scan_kernel(const float* __restrict__ pre, float* __restrict__ state,
                    const int* __restrict__ q_start, const int* __restrict__ slots,
                    T* __restrict__ out, int width) {
@@ -196,17 +203,19 @@ struct GatedStep {
     const float* softplus_lam;
     float decay_scale;
     int width;
-    __device__ __forceinline__ void operator()(int t, int c, float& a, float& b, float& o) const {
-        const float r = gates[(int64_t)t * 2 * width + c];
-        const float i = gates[(int64_t)t * 2 * width + width + c];
-        a = expf(-decay_scale * r * softplus_lam[c]);
-        b = sqrtf(1.f - a * a) * i * u[(int64_t)t * width + c];
-        o = gelu_tanh_f(pre[(int64_t)t * 2 * width + c]);
+    __device__ __forceinline__ void operator()(int t, int c, float& a, float& b, float& o,
+                                               bool with_gate) const {
+        const float r = __ldg(gates + (int64_t)t * 2 * width + c);
+        const float i = __ldg(gates + (int64_t)t * 2 * width + width + c);
+        const float x = __ldg(u + (int64_t)t * width + c);
+        a = expf(-decay_scale * r * __ldg(softplus_lam + c));
+        b = sqrtf(1.f - a * a) * i * x;
+        o = with_gate ? gelu_tanh_f(__ldg(pre + (int64_t)t * 2 * width + c)) : 0.f;
     }
 };
 
 template <typename T>
-__global__ void __launch_bounds__(SC_CHANNELS * SC_MAX_RUNS)
+__global__ void __launch_bounds__(1024)
 gated_recurrence_scan_kernel(const float* __restrict__ pre, const float* __restrict__ u,
                              const float* __restrict__ gates, const float* __restrict__ softplus_lam,
                              float decay_scale, float* __restrict__ state,
@@ -238,7 +247,7 @@ gated_recurrence_scan_kernel(const float* __restrict__ pre, const float* __restr
 using namespace mb;
 
 // Runs per sequence for a step whose longest portion has `max_q_len` tokens: about 16
-// tokens per run, at most SC_MAX_RUNS.
+// tokens per run, at most SC_MAX_RUNS (with 8 channels a block: 512 threads).
 static int scan_run_count(int max_q_len) {
     int runs = (max_q_len + 15) / 16;
     return runs < 1 ? 1 : (runs > SC_MAX_RUNS ? SC_MAX_RUNS : runs);

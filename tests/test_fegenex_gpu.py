@@ -164,7 +164,7 @@ def test_gated_recurrence_over_steps(ops, twin, dtype, width, blocks, taps):
 
 MIXED_CASES = [
     # heads, kv heads, dim, vdim, rot, page, q_lens, kv_lens, window, mix
-    (8, 8, 96, 48, 24, 16, (5, 1, 33), (5, 40, 33), 0, True),
+    (10, 5, 80, 40, 20, 16, (5, 1, 33), (5, 40, 33), 0, True),
     (4, 2, 32, 16, 16, 8, (1, 1, 1, 1), (1, 9, 24, 40), 0, True),
     (6, 1, 16, 40, 0, 16, (1, 17, 1), (300, 17, 64), 0, True),
     (3, 3, 24, 24, 8, 32, (40, 1, 2), (100, 77, 50), 24, True),

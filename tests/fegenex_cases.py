@@ -63,6 +63,13 @@ RAW = {
         _layer("attention", _attention(16, 4, 64, 80, rot=(32, 10000.0), v_mix=True), ff=256),
         _layer("attention", _attention(16, 4, 64, 80, rot=(64, 10000.0), v_mix=True)),
     ], positions=1200),
+    # nothing a multiple of 8: width, vocabulary, head sizes, feed-forward, recurrent widths
+    "odd": _model(100, 101, [
+        _layer("rglru", {"width": 60, "blocks": 3, "conv": 2}),
+        _layer("attention", _attention(3, 3, 20, 12, rot=(6, 123.0), v_mix=True), ff=130),
+        _layer("mingru", {"width": 52}, ff=34),
+        _layer("attention", _attention(6, 3, 20, 12, rot=(20, 9000.0), v_mix=True)),
+    ], positions=333, eps=1e-4),
 }
 SEED = {name: 11 + i for i, name in enumerate(RAW)}
 SHARPEN = 3.0     # q and k projections are scaled so that attention is far from uniform

@@ -13,7 +13,7 @@ from fegenex_cases import RAW, fegenex_model, make_runner, replay_and_compare, r
 from kernel_twins import TorchOps
 from plain_fegenex import plain_fegenex
 
-LENGTHS = {"mix": (37, 70, 129, 45, 3, 66), "ones": (33, 64, 150, 41, 90), "wide": (40, 70)}
+LENGTHS = {"mix": (37, 70, 129, 45, 3, 66), "ones": (33, 64, 150, 41, 90), "wide": (40, 70), "odd": (50, 7, 121, 33)}
 
 
 @pytest.mark.parametrize("name", ["only_mingru", "only_rglru", "only_attention", "only_ff"])
@@ -26,7 +26,7 @@ def test_each_layer_kind_alone(name):
                            steps, rows, 3e-5)
 
 
-@pytest.mark.parametrize("name", ["mix", "ones", "wide"])
+@pytest.mark.parametrize("name", ["mix", "ones", "wide", "odd"])
 @pytest.mark.parametrize("mode", ["whole", "decode_tail", "portions", "mixed"])
 def test_replay(name, mode):
     lengths = LENGTHS[name]

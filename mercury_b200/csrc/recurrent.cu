@@ -191,6 +191,71 @@ block_gates_kernel(const float* __restrict__ u, const float* __restrict__ w,
         }
 }
 
+// The same for the few tokens of a decode step, where the gate matrices have to be streamed
+// once and few blocks would do it slowly: a block computes 32 outputs (both kinds) of one
+// block b for up to 8 tokens, its four warps each taking a quarter of the inputs i; the
+// quarters are added in a fixed order through shared memory.
+__global__ void __launch_bounds__(128)
+block_gates_few_kernel(const float* __restrict__ u, const float* __restrict__ w,
+                       const float* __restrict__ bias, float* __restrict__ gates, int tokens,
+                       int width, int blocks, int size) {
+    grid_dependency_sync();
+    extern __shared__ __align__(16) float fs[];            // u: [size][8], then partial sums
+    float* u_s = fs;
+    float* part = fs + size * 8;                            // [4][2][8][32]
+    const int per = (size + 31) / 32;
+    const int otile = blockIdx.x % per;
+    const int b = blockIdx.x / per;
+    const int t0 = blockIdx.y * 8;
+    for (int idx = threadIdx.x; idx < 8 * size; idx += blockDim.x) {
+        const int tt = idx / size, i = idx - tt * size;
+        u_s[i * 8 + tt] = t0 + tt < tokens ? u[(int64_t)(t0 + tt) * width + b * size + i] : 0.f;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    const int o = otile * 32 + lane;
+    const int quarter = (size + 3) / 4;
+    const int i0 = slice * quarter, i1 = min(size, i0 + quarter);
+    float ar[8], ai[8];
+#pragma unroll
+    for (int tt = 0; tt < 8; ++tt) ar[tt] = ai[tt] = 0.f;
+    if (o < size) {
+        const float* wr = w + ((int64_t)b * size) * size + o;
+        const float* wi = w + ((int64_t)(blocks + b) * size) * size + o;
+#pragma unroll 8
+        for (int i = i0; i < i1; ++i) {
+            const float vr = __ldg(wr + (int64_t)i * size), vi = __ldg(wi + (int64_t)i * size);
+            const float4 x0 = *reinterpret_cast<const float4*>(u_s + i * 8);
+            const float4 x1 = *reinterpret_cast<const float4*>(u_s + i * 8 + 4);
+            ar[0] = fmaf(vr, x0.x, ar[0]); ar[1] = fmaf(vr, x0.y, ar[1]);
+            ar[2] = fmaf(vr, x0.z, ar[2]); ar[3] = fmaf(vr, x0.w, ar[3]);
+            ar[4] = fmaf(vr, x1.x, ar[4]); ar[5] = fmaf(vr, x1.y, ar[5]);
+            ar[6] = fmaf(vr, x1.z, ar[6]); ar[7] = fmaf(vr, x1.w, ar[7]);
+            ai[0] = fmaf(vi, x0.x, ai[0]); ai[1] = fmaf(vi, x0.y, ai[1]);
+            ai[2] = fmaf(vi, x0.z, ai[2]); ai[3] = fmaf(vi, x0.w, ai[3]);
+            ai[4] = fmaf(vi, x1.x, ai[4]); ai[5] = fmaf(vi, x1.y, ai[5]);
+            ai[6] = fmaf(vi, x1.z, ai[6]); ai[7] = fmaf(vi, x1.w, ai[7]);
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < 8; ++tt) {
+        part[((slice * 2 + 0) * 8 + tt) * 32 + lane] = ar[tt];
+        part[((slice * 2 + 1) * 8 + tt) * 32 + lane] = ai[tt];
+    }
+    __syncthreads();
+    // 2 kinds x 8 tokens x 32 outputs = 512 results, four per thread
+    for (int idx = threadIdx.x; idx < 2 * 8 * 32; idx += blockDim.x) {
+        const int l = idx & 31, tt = (idx >> 5) & 7, kind = idx >> 8;
+        const int oo = otile * 32 + l;
+        if (oo >= size || t0 + tt >= tokens) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int sl = 0; sl < 4; ++sl) v += part[((sl * 2 + kind) * 8 + tt) * 32 + l];
+        v += bias[(kind * blocks + b) * size + oo];
+        gates[(int64_t)(t0 + tt) * 2 * width + kind * width + b * size + oo] = sigmoid_f(v);
+    }
+}
+
 // pre: [tokens][2 * width] float32 = [branch y | convolution input x]; u: the convolution's
 // output; gates: [tokens][2 * width] = [r | i] after their sigmoids.
 // a = exp(-decay_scale * r * softplus_lam), S <- a S + sqrt(1 - a^2) * i * u, out = S * gelu(y).
@@ -291,27 +356,30 @@ MB_EXPORT int mb_block_gates(const float* u, const float* w, const float* bias, 
     if (tokens <= 0 || width <= 0) return MB_OK;
     if (blocks <= 0 || width % blocks || kinds != 2) return MB_ERR_UNSUPPORTED_SIZE;
     const int size = width / blocks;
-    const int tile = tokens <= 16 ? 8 : 32;
-    const size_t smem = (size_t)tile * size * sizeof(float);
+    const bool few = tokens <= 16;
+    const int tile = few ? 8 : 32;
+    const size_t smem = (size_t)tile * size * sizeof(float) + (few ? 4 * 2 * 8 * 32 * sizeof(float) : 0);
     if (smem > 200 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
     static size_t raised[2] = {0, 0};
-    size_t& mine = raised[tile == 8 ? 0 : 1];
+    size_t& mine = raised[few ? 0 : 1];
     if (smem > 48 * 1024 && smem > mine) {
-        const cudaError_t rc = tile == 8
-            ? cudaFuncSetAttribute(block_gates_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+        const cudaError_t rc = few
+            ? cudaFuncSetAttribute(block_gates_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
             : cudaFuncSetAttribute(block_gates_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (rc != cudaSuccess) return MB_ERR_UNSUPPORTED_SIZE;
         mine = smem;
     }
     const int rows = (tokens + tile - 1) / tile;
     if (rows > 65535) return MB_ERR_UNSUPPORTED_SIZE;
-    dim3 grid(((size + 127) / 128) * blocks, rows);
-    if (tile == 8)
-        MB_LAUNCH((block_gates_kernel<8>), grid, 128, smem, (cudaStream_t)stream, u, w, bias, gates,
+    if (few) {
+        dim3 grid(((size + 31) / 32) * blocks, rows);
+        MB_LAUNCH((block_gates_few_kernel), grid, 128, smem, (cudaStream_t)stream, u, w, bias, gates,
                   tokens, width, blocks, size);
-    else
+    } else {
+        dim3 grid(((size + 127) / 128) * blocks, rows);
         MB_LAUNCH((block_gates_kernel<32>), grid, 128, smem, (cudaStream_t)stream, u, w, bias, gates,
                   tokens, width, blocks, size);
+    }
     return launch_status();
 }
 

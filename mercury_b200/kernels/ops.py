@@ -655,8 +655,10 @@ class CudaOps:
             return max(1, self.decode_splits)
         bq = rows or max(1, min(64 // heads, 16, batch.max_q_len))
         blocks = batch.num_seqs * -(-batch.max_q_len // bq)
-        fill = max(1, min(self.mixed_head_max_splits,
-                          self.mixed_head_blocks_per_sm * self.sm_count // blocks))
+        # one row tile a sequence (a decode step): every block is as heavy as the others and
+        # the tensor-core kernel keeps one block on an SM, so one wave is the aim
+        per_sm = 1 if rows and batch.max_q_len <= rows else self.mixed_head_blocks_per_sm
+        fill = max(1, min(self.mixed_head_max_splits, per_sm * self.sm_count // blocks))
         if getattr(batch, "attention_splits", None):
             return fill
         key_tiles = -(-batch.max_kv_len // 32)

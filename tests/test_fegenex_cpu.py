@@ -89,3 +89,24 @@ def test_greedy_generation_through_the_engine():
     for prompt, out in zip(prompts, outs):
         assert out == greedy(raw, tensors, prompt, 6)
     assert engine.leaked_pages() == 0
+
+
+def test_preempted_requests_start_again_from_an_empty_state():
+    """A pool too small for all requests at once: the newest is put back (its pages and its
+    state slot given up) and recomputed later in a slot that another request has used; the
+    tokens stay the plain implementation's."""
+    from mercury_b200 import Engine, EngineConfig, SamplingParams
+
+    name = "ones"
+    raw, config, tensors = fegenex_model(name)
+    runner = make_runner(name, TorchOps(), "cpu", torch.float32, num_tokens=160, poison=True)
+    cfg = EngineConfig(model="(memory)", device="cpu", dtype="float32", block_size=16, num_blocks=10,
+                       max_running=4, max_batched_tokens=160, prefill_chunk=32, max_model_len=160,
+                       debug_invariants=True)
+    engine = Engine(cfg, runner=runner)
+    prompts = [requests_for(name, (33, 64, 41, 50))[f"r{i}"] for i in range(4)]
+    outs = engine.generate(prompts, SamplingParams(), 12)
+    for prompt, out in zip(prompts, outs):
+        assert out == greedy(raw, tensors, prompt, 12)
+    assert engine.snapshot()["scheduler"]["preemptions"] > 0
+    assert engine.leaked_pages() == 0

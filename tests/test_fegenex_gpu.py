@@ -177,6 +177,11 @@ MIXED_CASES = [
     (12, 2, 128, 128, 64, 16, (70, 2), (200, 66), 50, True),
     (32, 4, 32, 32, 16, 8, (20, 1), (90, 33), 0, True),
     (7, 7, 16, 8, 0, 16, (17, 1, 1), (17, 100, 1), 0, False),
+    # the remaining ways the tensor-core kernel divides heads over warps
+    (24, 8, 32, 64, 16, 16, (33, 1), (70, 300), 0, True),
+    (8, 2, 48, 48, 48, 16, (20, 2), (150, 66), 0, True),
+    (6, 2, 32, 96, 8, 32, (18, 1), (100, 45), 30, True),
+    (12, 4, 16, 24, 0, 16, (5, 40), (64, 40), 0, True),
 ]
 
 

@@ -70,6 +70,13 @@ RAW = {
         _layer("mingru", {"width": 52}, ff=34),
         _layer("attention", _attention(6, 3, 20, 12, rot=(20, 9000.0), v_mix=True)),
     ], positions=333, eps=1e-4),
+    # the layer sizes of a half-billion-parameter model (few layers, a small vocabulary)
+    "real": _model(896, 1000, [
+        _layer("attention", _attention(14, 2, 64, 64, rot=(32, 10000.0), v_mix=True), ff=4864),
+        _layer("mingru", {"width": 896}),
+        _layer("rglru", {"width": 896, "blocks": 7, "conv": 4}),
+        _layer("attention", _attention(14, 2, 64, 64, rot=(32, 10000.0), v_mix=True), ff=4864),
+    ], positions=1024),
 }
 SEED = {name: 11 + i for i, name in enumerate(RAW)}
 SHARPEN = 3.0     # q and k projections are scaled so that attention is far from uniform
@@ -80,7 +87,7 @@ def fegenex_model(name: str):
     """(raw config dictionary, typed config, {name: bfloat16 tensor})."""
     raw = RAW[name]
     _entry, config = config_from_dict(raw)
-    tensors = random_tensors(config, SEED[name], torch.bfloat16, std=0.08)
+    tensors = random_tensors(config, SEED[name], torch.bfloat16, std=0.03 if name == "real" else 0.08)
     for key in tensors:
         if key.endswith(".mix.q") or key.endswith(".mix.k"):
             tensors[key] = (tensors[key].float() * SHARPEN).to(torch.bfloat16)

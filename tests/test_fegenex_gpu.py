@@ -329,6 +329,19 @@ def test_replay(ops, dtype, name, mode):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("mode", ["whole", "mixed"])
+def test_real_layer_sizes(ops, dtype, mode):
+    """Width 896, 14 heads over 2 groups of 64, feed-forward 4864, recurrences of 896 channels:
+    the shapes at which the few-token, library and tensor-core kernels are chosen."""
+    name, lengths = "real", (150, 40, 300, 17)
+    requests = requests_for(name, lengths)
+    steps, rows = (replay_cases.whole(requests) if mode == "whole"
+                   else replay_cases.mixed(requests, 640, seed=5))
+    replay_and_compare(make_runner(name, ops, "cuda", dtype, num_tokens=640), name, lengths, steps,
+                       rows, tolerance_for(dtype, name, lengths))
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 def test_long_decoding_through_graphs(ops, dtype):
     """A short prompt and then 200 tokens one by one (replayed CUDA graphs in bfloat16 and
     float32 alike), over page borders and key tiles, logits wanted everywhere."""

@@ -9,6 +9,7 @@ from .model_config import (  # noqa: F401
     Architecture,
     ConfigError,
     FegenexConfig,
+    KinelixConfig,
     ModelConfig,
     Qwen2Config,
     architecture_named,

@@ -237,6 +237,138 @@ class FegenexConfig(ModelConfig):
         }
 
 
+# --------------------------------------------------------------------------- Kinelix
+
+_KINELIX_MIXER_KEYS = {
+    "mamba2": ("heads", "vdim", "state", "groups", "norm_groups", "conv"),
+    "delta": ("heads", "kv_heads", "dim", "vdim", "conv"),
+    "latent_attention": ("heads", "dim", "vdim", "kv_rank", "scale"),
+}
+
+
+@dataclass(frozen=True)
+class KinelixConfig(ModelConfig):
+    """A Kinelix decoder: pre-norm layers (layer norms with a weight and no bias, a learned
+    scale per feature on every sublayer's output), each with one of three mixers (a Mamba-2
+    state-space layer, a gated delta rule, attention over a cached low-rank latent with a
+    softmax sink and no positions) and a dense or routed feed-forward or none. config.json
+    keys: `architecture`, `width`, `vocab`, `embedding.scale`, `norm.eps`, `logit_softcap`
+    and `layers`, a list of `{"type", "mixer": {...}, "mlp": {"kind": "dense", "ff"} |
+    {"kind": "moe", "expert": {"ff"}, "router": {"experts", "top", "scale", "groups":
+    {"count", "keep"}}} | null}`. A latent-attention layer with `kv_from: j` has no
+    down-projection of its own and reads the latent rows that layer j caches. The design has
+    no positions, so nothing bounds a sequence's length but `max_positions` (not a key of
+    the design; absent, `DEFAULT_POSITIONS`)."""
+
+    width: int
+    vocab: int
+    norm_eps: float
+    embedding_scale: float = 1.0
+    logit_softcap: float = 0.0
+    max_positions: int = 1 << 20
+    layers: tuple = ()
+
+    DEFAULT_POSITIONS = 1 << 20
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "KinelixConfig":
+        def need(table: dict, key: str, where: str) -> Any:
+            if not isinstance(table, dict) or key not in table:
+                raise ConfigError(f"config.json has no {key!r} in {where}, which Kinelix needs")
+            return table[key]
+
+        def positive(table: dict, key: str, where: str) -> int:
+            value = int(need(table, key, where))
+            if value <= 0:
+                raise ConfigError(f"{where}: {key}={value} must be positive")
+            return value
+
+        layers = []
+        listed = need(raw, "layers", "the model")
+        for index, layer in enumerate(listed):
+            where = f"layer {index}"
+            kind = need(layer, "type", where)
+            if kind not in _KINELIX_MIXER_KEYS:
+                raise ConfigError(f"{where}: mixer type {kind!r} is not one of "
+                                  f"{', '.join(sorted(_KINELIX_MIXER_KEYS))}")
+            mixer = dict(need(layer, "mixer", where))
+            for key in _KINELIX_MIXER_KEYS[kind]:
+                if key != "scale":
+                    positive(mixer, key, f"{where}'s mixer")
+            if kind == "mamba2":
+                if int(mixer["heads"]) % int(mixer["groups"]):
+                    raise ConfigError(f"{where}: {mixer['heads']} heads do not divide into "
+                                      f"{mixer['groups']} groups")
+                if (int(mixer["heads"]) * int(mixer["vdim"])) % int(mixer["norm_groups"]):
+                    raise ConfigError(f"{where}: heads * vdim does not divide into "
+                                      f"{mixer['norm_groups']} norm groups")
+            if kind == "delta" and int(mixer["heads"]) % int(mixer["kv_heads"]):
+                raise ConfigError(f"{where}: {mixer['heads']} heads do not divide into "
+                                  f"{mixer['kv_heads']} query/key heads")
+            if kind == "latent_attention":
+                float(need(mixer, "scale", f"{where}'s mixer"))
+                source = mixer.get("kv_from")
+                if source is not None:
+                    source = int(source)
+                    ok = (0 <= source < index and listed[source].get("type") == "latent_attention"
+                          and listed[source].get("mixer", {}).get("kv_from") is None)
+                    if not ok:
+                        raise ConfigError(f"{where}: kv_from={source} must name an earlier "
+                                          f"latent-attention layer with a latent of its own")
+                    if int(listed[source]["mixer"].get("kv_rank", 0)) != int(mixer["kv_rank"]):
+                        raise ConfigError(f"{where}: kv_rank differs from layer {source}'s, "
+                                          f"whose latent it reads")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                mlp = dict(mlp)
+                what = need(mlp, "kind", f"{where}'s mlp")
+                if what == "dense":
+                    positive(mlp, "ff", f"{where}'s mlp")
+                elif what == "moe":
+                    positive(need(mlp, "expert", f"{where}'s mlp"), "ff", f"{where}'s expert")
+                    router = dict(need(mlp, "router", f"{where}'s mlp"))
+                    experts = positive(router, "experts", f"{where}'s router")
+                    top = positive(router, "top", f"{where}'s router")
+                    float(need(router, "scale", f"{where}'s router"))
+                    groups = router.get("groups") or {"count": 1, "keep": 1}
+                    count = positive(groups, "count", f"{where}'s router groups")
+                    keep = positive(groups, "keep", f"{where}'s router groups")
+                    if experts % count or keep > count or top > keep * (experts // count):
+                        raise ConfigError(f"{where}: {experts} experts in {count} groups of which "
+                                          f"{keep} are kept cannot give {top} experts a token")
+                else:
+                    raise ConfigError(f"{where}: feed-forward kind {what!r} is not built")
+            layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+        if not layers:
+            raise ConfigError("config.json lists no layers")
+        return cls(
+            architecture=str(raw.get("architecture") or (raw.get("architectures") or ["Kinelix"])[0]),
+            width=positive(raw, "width", "the model"),
+            vocab=positive(raw, "vocab", "the model"),
+            norm_eps=float(need(need(raw, "norm", "the model"), "eps", "norm")),
+            embedding_scale=float((raw.get("embedding") or {}).get("scale", 1.0)),
+            logit_softcap=float(raw.get("logit_softcap") or 0.0),
+            max_positions=int(raw.get("max_positions") or cls.DEFAULT_POSITIONS),
+            layers=tuple(layers),
+        )
+
+    def to_dict(self) -> dict:
+        import copy
+
+        out = {
+            "architecture": self.architecture,
+            "width": self.width,
+            "vocab": self.vocab,
+            "embedding": {"scale": self.embedding_scale},
+            "norm": {"eps": self.norm_eps},
+            "logit_softcap": self.logit_softcap,
+            "layers": [copy.deepcopy(l) for l in self.layers],
+        }
+        if self.max_positions != self.DEFAULT_POSITIONS:
+            out["max_positions"] = self.max_positions
+        return out
+
+
 # --------------------------------------------------------------------------- the registry
 
 @dataclass(frozen=True)

@@ -128,7 +128,12 @@ class ModelRunner:
         for cache_id, layer in self.model.cache_layers.items():
             pages = self.cache.pools[layer.group].num_pages
             need = layer.need
-            if need.value_head_dim == need.head_dim:
+            if need.shared_values:
+                # one row per token is key and value at once: a single tensor, handed out twice
+                store = torch.zeros((pages, need.num_kv_heads, page_size, need.head_dim),
+                                    dtype=dtype, device=self.device)
+                self.kv_layers[cache_id] = (store, store)
+            elif need.value_head_dim == need.head_dim:
                 store = torch.zeros((2, pages, need.num_kv_heads, page_size, need.head_dim),
                                     dtype=dtype, device=self.device)
                 self.kv_layers[cache_id] = (store[0], store[1])
@@ -186,8 +191,7 @@ class ModelRunner:
         """Bytes of keys and values one token occupies over all cache layers
         (mercury/config.py:73-81)."""
         elem = torch.finfo(self.dtype).bits // 8
-        return sum(l.need.num_kv_heads * (l.need.head_dim + l.need.value_head_dim) * elem
-                   for l in self.model.cache_layers.values())
+        return sum(_row_elements(l.need) * elem for l in self.model.cache_layers.values())
 
     # ------------------------------------------------------------------ sequences
 
@@ -433,10 +437,16 @@ class ModelRunner:
         return logits
 
 
+def _row_elements(need) -> int:
+    """Elements one token occupies in a cache layer."""
+    if need.shared_values:
+        return need.num_kv_heads * need.head_dim
+    return need.num_kv_heads * (need.head_dim + need.value_head_dim)
+
+
 def kv_bytes_per_token_of(folder, dtype: torch.dtype) -> int:
     """Cache bytes per token of the model under `folder`, without loading its weights."""
     entry, config = read_model_config(folder)
     model = Model(entry.describe(config))
     elem = torch.finfo(dtype).bits // 8
-    return sum(l.need.num_kv_heads * (l.need.head_dim + l.need.value_head_dim) * elem
-               for l in model.cache_layers.values())
+    return sum(_row_elements(l.need) * elem for l in model.cache_layers.values())

@@ -240,4 +240,84 @@ class MixedHeadAttention(Mixer):
         return out
 
 
+class LatentAttention(Mixer):
+    """Attention over a cached low-rank latent, without positions, with a softmax sink.
+
+    Per token: q = Wq h (heads x dim); c = rmsnorm(Wdkv h) * w, `rank` numbers, the only
+    thing the cache keeps; per head k = Wuk c and v = Wuv c; weights = exp(s_j) / (sum_j'
+    exp(s_j') + exp(sink_h)) over the keys j <= p with s = q.k * scale; an output projection.
+
+    The keys and values are never built. Since q.(Wuk_h c) = (Wuk_h^T q).c, a head's query is
+    taken into the latent space once per token and the head attends over the cached rows
+    themselves, which serve as keys and as values (one shared head of size `rank` for all
+    query heads); Wuv_h is applied to the head's weighted sum of rows afterwards.
+
+    `own_latent=False`: the layer has no Wdkv and reads the rows that another layer's call
+    stored (its `LayerCall` names that call's cache layer with `writes_cache=False`).
+    """
+
+    capturable = True
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, value_dim: int, rank: int,
+                 scale: float, eps: float, prefix: str, own_latent: bool = True,
+                 names: dict | None = None):
+        self.hidden_size, self.num_heads = hidden_size, num_heads
+        self.head_dim, self.value_dim, self.rank = head_dim, value_dim, rank
+        self.scale, self.eps, self.prefix = float(scale), float(eps), prefix
+        self.own_latent = bool(own_latent)
+        self.q_size = num_heads * head_dim
+        self.names = {"q": "q", "down": "dkv", "down_norm": "dkv.norm", "up_k": "uk", "up_v": "uv",
+                      "sink": "sink", "o": "o"}
+        self.names.update(names or {})
+
+    def cache_need(self):
+        return CacheNeed(1, self.rank, 0, shared_values=True)
+
+    def tensor_specs(self):
+        p, n, h = self.prefix, self.names, self.hidden_size
+        specs = [TensorSpec(p + n["q"], (self.q_size, h))]
+        if self.own_latent:
+            specs += [TensorSpec(p + n["down"], (self.rank, h)),
+                      TensorSpec(p + n["down_norm"], (self.rank,), init="ones_normal", std=0.05)]
+        return specs + [TensorSpec(p + n["up_k"], (self.q_size, self.rank)),
+                        TensorSpec(p + n["up_v"], (self.num_heads * self.value_dim, self.rank)),
+                        TensorSpec(p + n["sink"], (self.num_heads,), std=1.0),
+                        TensorSpec(p + n["o"], (h, self.num_heads * self.value_dim))]
+
+    def load(self, tensors, setup):
+        p, n = self.prefix, self.names
+        mats = [setup.place(tensors[p + n["q"]])]
+        if self.own_latent:
+            mats.append(setup.place(tensors[p + n["down"]]))
+            self.down_norm = setup.place(tensors[p + n["down_norm"]])
+        widest = torch.float32 if any(t.dtype == torch.float32 for t in mats) else mats[0].dtype
+        self.in_weight = torch.cat([t.to(widest) for t in mats], dim=0).contiguous()   # rows [q; dkv]
+        up_k = setup.place(tensors[p + n["up_k"]])
+        # per head [rank, dim]: the transposed up-projection, which takes a query to the latent
+        self.absorb = up_k.view(self.num_heads, self.head_dim, self.rank).transpose(1, 2).contiguous()
+        self.up_v = setup.place(tensors[p + n["up_v"]]).view(self.num_heads, self.value_dim, self.rank)
+        self.sink = setup.place(tensors[p + n["sink"]]).float().contiguous()
+        self.out_weight = setup.place(tensors[p + n["o"]])
+
+    def forward(self, x, ctx, cache, state):
+        tokens, ops = x.shape[0], ctx.ops
+        if cache.write != self.own_latent:
+            raise ValueError(f"{self.prefix}: a layer stores latent rows iff it makes its own")
+        pre = ctx.buffer("latent_in", tokens, self.in_weight.shape[0], dtype="float32")
+        ops.linear(x, self.in_weight, None, pre)
+        if self.own_latent:
+            ops.latent_norm_store(pre, self.q_size, self.rank, self.down_norm, self.eps, ctx.batch, cache)
+        q = ctx.buffer("latent_q", tokens, self.num_heads * self.rank)
+        ops.head_linear(pre, 0, self.absorb, q)
+        gathered = ctx.buffer("latent_sum", tokens, self.num_heads * self.rank)
+        ops.paged_attention(q, self.num_heads, 1, self.rank, ctx.batch, cache, self.scale, 0,
+                            gathered, sinks=self.sink)
+        attended = ctx.buffer("attended_v", tokens, self.num_heads * self.value_dim)
+        ops.head_linear(gathered, 0, self.up_v, attended)
+        out = ctx.buffer("sublayer_out", tokens, self.hidden_size, dtype="float32")
+        ops.linear(attended, self.out_weight, None, out)
+        return out
+
+
 register_mixer("mixed_head_attention", MixedHeadAttention)
+register_mixer("latent_attention", LatentAttention)

@@ -99,12 +99,15 @@ class PartSpec:
 class CacheNeed:
     """Keys and values a mixer keeps per token. `window` = 0 keeps every key; a positive
     window keeps the last `window` (pages behind it are given back). `value_dim` is the
-    size of a value head where it differs from the key head's (0: the same)."""
+    size of a value head where it differs from the key head's (0: the same). With
+    `shared_values` one row per token serves as key and as value (a cached latent): no value
+    pages exist and a mixer is handed the key pages in their place."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
     value_dim: int = 0
+    shared_values: bool = False
 
     @property
     def value_head_dim(self) -> int:

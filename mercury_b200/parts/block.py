@@ -7,7 +7,8 @@ delta that is still to be added to it, and returns the delta it leaves behind.
 
 from __future__ import annotations
 
-from .base import PartSpec, build_part, register_arrangement
+from .base import Part, PartSpec, TensorSpec, build_part, register_arrangement
+from .norm import scaled_add
 
 
 class PreNormBlock:
@@ -90,5 +91,68 @@ class SandwichBlock:
         return None
 
 
+class LayerScale(Part):
+    """One learned number per feature that a sublayer's output is multiplied by before it
+    joins the stream."""
+
+    capturable = True
+
+    def __init__(self, size: int, weight_name: str, init_std: float = 0.1):
+        self.size, self.weight_name, self.init_std = size, weight_name, init_std
+        self.weight = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.weight_name, (self.size,), init="ones_normal", std=self.init_std)]
+
+    def load(self, tensors, setup):
+        self.weight = setup.place(tensors[self.weight_name])
+
+
+class LayerScaleBlock:
+    """Pre-norm with a learned scale on every sublayer's output: h <- h + s1 * mixer(norm1(h)),
+    then, where the block has a feed-forward, h <- h + s2 * ff(norm2(h)). The sums are made at
+    once (the block leaves no pending delta), each by the kernel that also computes the norm
+    that comes next."""
+
+    def __init__(self, hidden_size: int, mixer: PartSpec, mixer_norm: PartSpec, mixer_scale: str,
+                 feed_forward: PartSpec | None = None, feed_forward_norm: PartSpec | None = None,
+                 feed_forward_scale: str | None = None):
+        self.mixer = build_part("mixer", mixer)
+        self.mixer_norm = build_part("norm", mixer_norm)
+        self.mixer_scale = LayerScale(hidden_size, mixer_scale)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_scale = None
+        if feed_forward is not None:
+            if feed_forward_norm is None or feed_forward_scale is None:
+                raise ValueError("a feed-forward needs its norm and its scale")
+            self.feed_forward = build_part("feed_forward", feed_forward)
+            self.feed_forward_norm = build_part("norm", feed_forward_norm)
+            self.feed_forward_scale = LayerScale(hidden_size, feed_forward_scale)
+
+    def mixers(self):
+        return [self.mixer]
+
+    def parts(self):
+        out = [self.mixer_norm, self.mixer, self.mixer_scale]
+        if self.feed_forward is not None:
+            out += [self.feed_forward_norm, self.feed_forward, self.feed_forward_scale]
+        return out
+
+    def first_norm(self):
+        return self.mixer_norm
+
+    def forward(self, h, delta, ctx, caches, states, next_norm=None):
+        x = self.mixer_norm.add_norm(h, delta, ctx)
+        mixed = self.mixer.forward(x, ctx, caches[0], states[0])
+        if self.feed_forward is None:
+            scaled_add(h, mixed, self.mixer_scale.weight, ctx, then_norm=next_norm)
+            return None
+        scaled_add(h, mixed, self.mixer_scale.weight, ctx, then_norm=self.feed_forward_norm)
+        x = self.feed_forward_norm.add_norm(h, None, ctx)
+        scaled_add(h, self.feed_forward.forward(x, ctx), self.feed_forward_scale.weight, ctx,
+                   then_norm=next_norm)
+        return None
+
+
 register_arrangement("pre_norm", PreNormBlock)
+register_arrangement("pre_norm_layer_scale", LayerScaleBlock)
 register_arrangement("sandwich_norm", SandwichBlock)

@@ -19,10 +19,12 @@ from .base import Embedding, Head, TensorSpec, register_embedding, register_head
 class TokenEmbedding(Embedding):
     capturable = True
 
-    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str):
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str, scale: float = 1.0):
+        """`scale`: every row is multiplied by it on its way into the stream."""
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         self.weight_name = weight_name
+        self.scale = float(scale)
         self.table = None
 
     def tensor_specs(self):
@@ -33,7 +35,10 @@ class TokenEmbedding(Embedding):
 
     def forward(self, token_ids, ctx):
         h = ctx.buffer("residual", token_ids.shape[0], self.hidden_size, dtype="float32")
-        ctx.ops.embed(token_ids, self.table, h)
+        if self.scale != 1.0:
+            ctx.ops.embed(token_ids, self.table, h, scale=self.scale)
+        else:
+            ctx.ops.embed(token_ids, self.table, h)
         return h
 
 
@@ -84,6 +89,21 @@ class LinearHead(Head):
         return logits
 
 
+class SoftCappedHead(LinearHead):
+    """logits <- cap * tanh(logits / cap) behind the product (`cap` 0: none)."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str, cap: float):
+        super().__init__(vocab_size, hidden_size, weight_name)
+        self.cap = float(cap)
+
+    def forward(self, rows, ctx):
+        logits = super().forward(rows, ctx)
+        if self.cap > 0.0:
+            ctx.ops.softcap(logits, self.cap)
+        return logits
+
+
 register_embedding("lookup", TokenEmbedding)
 register_embedding("lookup_learned_positions", PositionedEmbedding)
 register_head("linear", LinearHead)
+register_head("linear_softcap", SoftCappedHead)

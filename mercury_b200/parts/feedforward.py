@@ -20,7 +20,10 @@ class GatedFeedForward(FeedForward):
 
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str,
                  activation: str = "silu",
-                 names: tuple = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+                 names: tuple = ("gate_proj.weight", "up_proj.weight", "down_proj.weight"),
+                 float_out: bool = False):
+        """`float_out`: the result is left in float32 (from the down-projection's accumulators)
+        for a block that scales it before the sum; such a block makes the sum itself."""
         if activation not in self.ACTIVATIONS:
             raise ValueError(f"activation {activation!r} is not built; only "
                              f"{' and '.join(self.ACTIVATIONS)}")
@@ -29,8 +32,9 @@ class GatedFeedForward(FeedForward):
         self.prefix = prefix
         self.activation = activation
         self.names = tuple(names)
+        self.float_out = bool(float_out)
         # the fused products that add into the stream belong to the pre-norm block
-        if activation != "silu":
+        if activation != "silu" or self.float_out:
             self.adds_to_residual = False
             self.accepts_pending_norm = False
         self.gate_up_weight = self.down_weight = None
@@ -61,6 +65,10 @@ class GatedFeedForward(FeedForward):
             ctx.ops.linear(act, self.down_weight, None, out)
             return out
         ctx.ops.linear_swiglu(x, self.gate_up_weight, act, ctx, ahead=self.down_weight)
+        if self.float_out:
+            out = ctx.buffer("sublayer_out", tokens, self.hidden_size, dtype="float32")
+            ctx.ops.linear(act, self.down_weight, None, out)
+            return out
         if residual is not None:
             return ctx.ops.linear_residual(act, self.down_weight, None, residual, ctx, "ff_out",
                                            then_norm=then_norm)
@@ -69,4 +77,72 @@ class GatedFeedForward(FeedForward):
         return out
 
 
+class RoutedExperts(FeedForward):
+    """A mixture of SiLU-gated experts, of which each token uses `top`.
+
+    Router: z = Wr x in float32, s = sigmoid(z). The choice is made on s + correction (a
+    learned number per expert that steers the choice and nothing else): the experts form
+    `group_count` equal groups of neighbours, a group's score is the sum of its two largest
+    choice scores, only experts of the best `group_keep` groups can be chosen, and of those
+    the `top` with the largest choice scores are. A chosen expert's weight is its s times
+    `route_scale`; the weights are not renormalised. out = sum of weight_e * expert_e(x).
+
+    The experts' matrices are held stacked, `[experts, 2 ff, hidden]` (gate rows, then up
+    rows) and `[experts, hidden, ff]`, so that one grouped product serves all of them.
+    """
+
+    capturable = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int,
+                 route_scale: float, prefix: str, group_count: int = 1, group_keep: int = 1,
+                 names: dict | None = None):
+        if experts % group_count or group_keep > group_count:
+            raise ValueError(f"{experts} experts do not form {group_count} groups of which "
+                             f"{group_keep} are kept")
+        if top > group_keep * (experts // group_count):
+            raise ValueError(f"{top} experts cannot be chosen from {group_keep} groups of "
+                             f"{experts // group_count}")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.experts, self.top, self.route_scale = experts, top, float(route_scale)
+        self.group_count, self.group_keep, self.prefix = group_count, group_keep, prefix
+        self.names = {"expert": "e{}.", "gate": "gate", "up": "up", "down": "down",
+                      "router": "router", "correction": "correction"}
+        self.names.update(names or {})
+
+    def _expert(self, index: int, which: str) -> str:
+        return self.prefix + self.names["expert"].format(index) + self.names[which]
+
+    def tensor_specs(self):
+        h, f = self.hidden_size, self.intermediate_size
+        specs = []
+        for e in range(self.experts):
+            specs += [TensorSpec(self._expert(e, "gate"), (f, h)), TensorSpec(self._expert(e, "up"), (f, h)),
+                      TensorSpec(self._expert(e, "down"), (h, f))]
+        return specs + [TensorSpec(self.prefix + self.names["router"], (self.experts, h), std=0.2),
+                        TensorSpec(self.prefix + self.names["correction"], (self.experts,), std=0.2)]
+
+    def load(self, tensors, setup):
+        placed = [[setup.place(tensors[self._expert(e, which)]) for which in ("gate", "up", "down")]
+                  for e in range(self.experts)]
+        widest = (torch.float32 if any(t.dtype == torch.float32 for row in placed for t in row)
+                  else placed[0][0].dtype)
+        self.gate_up_weight = torch.stack([torch.cat([g.to(widest), u.to(widest)], dim=0)
+                                           for g, u, _d in placed]).contiguous()
+        self.down_weight = torch.stack([d.to(widest) for _g, _u, d in placed]).contiguous()
+        # the router is float32 in both engines
+        self.router = setup.place(tensors[self.prefix + self.names["router"]]).float().contiguous()
+        self.correction = setup.place(tensors[self.prefix + self.names["correction"]]).float().contiguous()
+
+    def forward(self, x, ctx):
+        tokens, ops = x.shape[0], ctx.ops
+        chosen = ctx.buffer("route_experts", tokens, self.top, dtype=torch.int32)
+        weights = ctx.buffer("route_weights", tokens, self.top, dtype="float32")
+        ops.route_experts(x, self.router, self.correction, self.group_count, self.group_keep,
+                          self.route_scale, chosen, weights)
+        out = ctx.buffer("sublayer_out", tokens, self.hidden_size, dtype="float32")
+        ops.expert_feed_forward(x, chosen, weights, self.gate_up_weight, self.down_weight, out, ctx)
+        return out
+
+
 register_feed_forward("gated", GatedFeedForward)
+register_feed_forward("routed_experts", RoutedExperts)

@@ -113,5 +113,53 @@ class RMSNorm(Norm):
         return out
 
 
+class LayerNorm(Norm):
+    """(x - mean) / sqrt(var + eps) * w with a weight and no bias; mean and variance (the mean
+    of the squared deviations) in float32 over the float32 stream. `add_norm` is the
+    interface every norm has; `scaled_add` joins a sublayer's output to the stream under a
+    per-feature scale and computes the norm that follows in the same kernel."""
+
+    capturable = True
+    center = True
+
+    def __init__(self, size: int, eps: float, weight_name: str, init_std: float = 0.05):
+        self.size = size
+        self.eps = eps
+        self.weight_name = weight_name
+        self.init_std = init_std
+        self.weight = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.weight_name, (self.size,), init="ones_normal", std=self.init_std)]
+
+    def load(self, tensors, setup):
+        self.weight = setup.place(tensors[self.weight_name])
+
+    def add_norm(self, h, delta, ctx, rows=None, defer=False):
+        pre = getattr(ctx, "prenormed", None)
+        if pre is not None:
+            ctx.prenormed = None
+            if pre[0] is self and delta is None and rows is None:
+                return pre[1].materialize()
+        count = h.shape[0] if rows is None else rows.shape[0]
+        out = ctx.buffer("normed" if rows is None else "normed_rows", count, self.size)
+        ctx.ops.scaled_add_norm(h, delta, None, self.weight, self.eps, True, out, rows)
+        return out
+
+
+def scaled_add(h, delta, scale, ctx, then_norm=None):
+    """h <- h + scale * delta in the float32 stream (`scale` one number per feature, or None).
+    With `then_norm` (a `LayerNorm` or `RMSNorm` over the stream's width) the same kernel
+    leaves that norm's output of the new stream in `ctx.prenormed`."""
+    follow = then_norm if isinstance(then_norm, (LayerNorm, RMSNorm)) and then_norm.size == h.shape[1] else None
+    out = ctx.buffer("normed", h.shape[0], h.shape[1]) if follow is not None else None
+    ctx.ops.scaled_add_norm(h, delta, scale,
+                            follow.weight if follow is not None else None,
+                            follow.eps if follow is not None else 0.0,
+                            bool(getattr(follow, "center", False)), out, None)
+    ctx.prenormed = (follow, Computed(out)) if follow is not None else None
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)
 register_norm("rmsnorm_scalar", lambda **params: RMSNorm(gain="scalar", **params))

@@ -14,6 +14,20 @@ Linear Recurrences with Local Attention for Efficient Language Models"):
            i = sigmoid(Ri_b u_b + ri_b); a = exp(-decay_scale * r * softplus(lam));
            S_t = a S_{t-1} + sqrt(1 - a^2) * i * u;  out = Wo (S_t * y).
            Its state is S and the last taps - 1 inputs of the convolution.
+`Mamba2` (Dao and Gu, "Transformers are SSMs: Generalized Models and Efficient Algorithms
+Through Structured State Space Duality"): [z | x | B | C | dt] = W_in h; (x, B, C) through a
+           causal convolution with bias and SiLU; dt = softplus(dt + dt_bias); per head, with
+           B and C of the head's group, S_t = exp(-exp(A_log) dt_t) S_{t-1} + dt_t B_t x_t^T
+           (S is state x head_dim), y_t = S_t^T C_t + D x_t; out = Wo (groupnorm(y * silu(z)) * w),
+           the norm an RMS norm over each of `norm_groups` equal parts.
+`GatedDeltaRule` (Yang, Kautz and Hatamizadeh, "Gated Delta Networks: Improving Mamba2 with
+Delta Rule"): q, k, v through causal convolutions and SiLU; q, k to unit length per head, q
+           also times key_dim^-1/2; beta = sigmoid(Wb h), g = exp(-exp(A_log) softplus(Wa h +
+           dt_bias)); S <- g S, u = beta (v - S^T k), S <- S + k u^T, o = S^T q (the read-out
+           sees the token's own write; S is key_dim x head_dim); out = Wo (o / rms(o) * w *
+           silu(Wg h)).
+Both keep S and the last taps - 1 inputs of their convolutions in one state row per
+request: [S | inputs one token back | two tokens back | ...].
 """
 
 from __future__ import annotations
@@ -135,5 +149,150 @@ class GatedLinearRecurrence(Mixer):
         return out
 
 
+def _float(setup, tensor):
+    """What stands inside a recurrence is float32 in both engines."""
+    return setup.place(tensor).float().contiguous()
+
+
+class Mamba2(Mixer):
+    capturable = True
+
+    def __init__(self, hidden_size: int, heads: int, head_dim: int, state_size: int, groups: int,
+                 norm_groups: int, taps: int, eps: float, prefix: str, names: dict | None = None):
+        if heads % groups:
+            raise ValueError(f"{heads} heads do not divide into {groups} groups")
+        if (heads * head_dim) % norm_groups:
+            raise ValueError(f"{heads * head_dim} channels do not divide into {norm_groups} norm groups")
+        if not 1 <= taps <= 16:
+            raise ValueError(f"a convolution over {taps} tokens is not built (1 to 16)")
+        self.hidden_size, self.heads, self.head_dim = hidden_size, heads, head_dim
+        self.state_size, self.groups, self.norm_groups, self.taps = state_size, groups, norm_groups, taps
+        self.eps, self.prefix = float(eps), prefix
+        self.inner = heads * head_dim
+        self.channels = self.inner + 2 * groups * state_size        # what the convolution sees
+        self.proj = 2 * self.inner + 2 * groups * state_size + heads
+        self.cells = heads * state_size * head_dim
+        self.names = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "dt_bias": "dt_bias",
+                      "A_log": "A_log", "D": "D", "norm": "norm", "o": "o"}
+        self.names.update(names or {})
+
+    def state_need(self):
+        return StateNeed((self.cells + (self.taps - 1) * self.channels,), torch.float32)
+
+    def tensor_specs(self):
+        p, n = self.prefix, self.names
+        return [TensorSpec(p + n["in"], (self.proj, self.hidden_size)),
+                TensorSpec(p + n["conv"], (self.channels, self.taps), std=0.3),
+                TensorSpec(p + n["conv_bias"], (self.channels,)),
+                TensorSpec(p + n["dt_bias"], (self.heads,), std=0.5, mean=-0.5),
+                TensorSpec(p + n["A_log"], (self.heads,), std=0.5),
+                TensorSpec(p + n["D"], (self.heads,), init="ones_normal", std=0.1),
+                TensorSpec(p + n["norm"], (self.inner,), init="ones_normal", std=0.05),
+                TensorSpec(p + n["o"], (self.hidden_size, self.inner))]
+
+    def load(self, tensors, setup):
+        p, n = self.prefix, self.names
+        self.in_weight = setup.place(tensors[p + n["in"]])
+        self.conv = _float(setup, tensors[p + n["conv"]])
+        self.conv_bias = _float(setup, tensors[p + n["conv_bias"]])
+        self.dt_bias = _float(setup, tensors[p + n["dt_bias"]])
+        self.neg_rate = (-torch.exp(_float(setup, tensors[p + n["A_log"]]))).contiguous()
+        self.skip = _float(setup, tensors[p + n["D"]])
+        self.norm_weight = _float(setup, tensors[p + n["norm"]])
+        self.out_weight = setup.place(tensors[p + n["o"]])
+
+    def forward(self, x, ctx, cache, state):
+        tokens, ops = x.shape[0], ctx.ops
+        pre = ctx.buffer("recurrent_in", tokens, self.proj, dtype="float32")
+        ops.linear(x, self.in_weight, None, pre)
+        cells, tail = state[:, :self.cells], state[:, self.cells:]
+        xbc = ctx.buffer("recurrent_conv", tokens, self.channels, dtype="float32")
+        ops.conv_act(pre, self.inner, self.conv, self.conv_bias, tail, ctx.batch, xbc, "silu")
+        ops.conv_tail_update(pre, self.inner, self.channels, self.taps, tail, ctx.batch)
+        y = ctx.buffer("recurrent_y", tokens, self.inner, dtype="float32")
+        ops.mamba2_scan(xbc, pre, self.proj - self.heads, self.dt_bias, self.neg_rate, self.skip,
+                        (self.heads, self.head_dim, self.state_size, self.groups), cells,
+                        ctx.batch, y)
+        mixed = ctx.buffer("recurrent_mixed", tokens, self.inner)
+        ops.gated_group_norm(y, pre, 0, self.norm_weight, self.norm_groups, self.eps, True, mixed)
+        out = ctx.buffer("sublayer_out", tokens, self.hidden_size, dtype="float32")
+        ops.linear(mixed, self.out_weight, None, out)
+        return out
+
+
+class GatedDeltaRule(Mixer):
+    capturable = True
+
+    def __init__(self, hidden_size: int, heads: int, key_heads: int, key_dim: int, head_dim: int,
+                 taps: int, eps: float, prefix: str, unit_eps: float = 1e-6,
+                 names: dict | None = None):
+        if heads % key_heads:
+            raise ValueError(f"{heads} heads do not divide into {key_heads} query/key heads")
+        if not 1 <= taps <= 16:
+            raise ValueError(f"a convolution over {taps} tokens is not built (1 to 16)")
+        self.hidden_size, self.heads, self.key_heads = hidden_size, heads, key_heads
+        self.key_dim, self.head_dim, self.taps = key_dim, head_dim, taps
+        self.eps, self.unit_eps, self.prefix = float(eps), float(unit_eps), prefix
+        self.qk = key_heads * key_dim
+        self.inner = heads * head_dim
+        self.channels = 2 * self.qk + self.inner                  # [q | k | v]
+        self.proj = self.channels + self.inner + 2 * heads         # ... | g | b | a
+        self.cells = heads * key_dim * head_dim
+        self.names = {"q": "q", "k": "k", "v": "v", "conv": ".conv", "b": "b", "a": "a", "g": "g",
+                      "dt_bias": "dt_bias", "A_log": "A_log", "norm": "norm", "o": "o"}
+        self.names.update(names or {})
+
+    def state_need(self):
+        return StateNeed((self.cells + (self.taps - 1) * self.channels,), torch.float32)
+
+    def tensor_specs(self):
+        p, n, h = self.prefix, self.names, self.hidden_size
+        specs = []
+        for key, rows in (("q", self.qk), ("k", self.qk), ("v", self.inner)):
+            specs += [TensorSpec(p + n[key], (rows, h)),
+                      TensorSpec(p + n[key] + n["conv"], (rows, self.taps), std=0.3)]
+        return specs + [TensorSpec(p + n["b"], (self.heads, h)), TensorSpec(p + n["a"], (self.heads, h)),
+                        TensorSpec(p + n["g"], (self.inner, h)),
+                        TensorSpec(p + n["dt_bias"], (self.heads,), std=0.5, mean=-0.5),
+                        TensorSpec(p + n["A_log"], (self.heads,), std=0.5),
+                        TensorSpec(p + n["norm"], (self.head_dim,), init="ones_normal", std=0.05),
+                        TensorSpec(p + n["o"], (h, self.inner))]
+
+    def load(self, tensors, setup):
+        p, n = self.prefix, self.names
+        mats = [setup.place(tensors[p + n[key]]) for key in ("q", "k", "v", "g", "b", "a")]
+        widest = torch.float32 if any(t.dtype == torch.float32 for t in mats) else mats[0].dtype
+        # one product feeds everything that is read off the layer's input: rows [q; k; v; g; b; a]
+        self.in_weight = torch.cat([t.to(widest) for t in mats], dim=0).contiguous()
+        self.conv = torch.cat([_float(setup, tensors[p + n[key] + n["conv"]])
+                               for key in ("q", "k", "v")], dim=0).contiguous()
+        self.dt_bias = _float(setup, tensors[p + n["dt_bias"]])
+        self.neg_rate = (-torch.exp(_float(setup, tensors[p + n["A_log"]]))).contiguous()
+        self.norm_weight = _float(setup, tensors[p + n["norm"]])
+        self.out_weight = setup.place(tensors[p + n["o"]])
+
+    def forward(self, x, ctx, cache, state):
+        tokens, ops = x.shape[0], ctx.ops
+        pre = ctx.buffer("recurrent_in", tokens, self.proj, dtype="float32")
+        ops.linear(x, self.in_weight, None, pre)
+        cells, tail = state[:, :self.cells], state[:, self.cells:]
+        qkv = ctx.buffer("recurrent_conv", tokens, self.channels, dtype="float32")
+        ops.conv_act(pre, 0, self.conv, None, tail, ctx.batch, qkv, "silu")
+        ops.conv_tail_update(pre, 0, self.channels, self.taps, tail, ctx.batch)
+        o = ctx.buffer("recurrent_y", tokens, self.inner, dtype="float32")
+        gate_at = self.channels
+        ops.delta_rule_scan(qkv, pre, gate_at + self.inner, gate_at + self.inner + self.heads,
+                            self.dt_bias, self.neg_rate,
+                            (self.heads, self.key_heads, self.key_dim, self.head_dim),
+                            self.unit_eps, cells, ctx.batch, o)
+        mixed = ctx.buffer("recurrent_mixed", tokens, self.inner)
+        ops.gated_group_norm(o, pre, gate_at, self.norm_weight, self.heads, self.eps, False, mixed)
+        out = ctx.buffer("sublayer_out", tokens, self.hidden_size, dtype="float32")
+        ops.linear(mixed, self.out_weight, None, out)
+        return out
+
+
 register_mixer("mingru", MinGRU)
+register_mixer("mamba2", Mamba2)
+register_mixer("gated_delta_rule", GatedDeltaRule)
 register_mixer("gated_linear_recurrence", GatedLinearRecurrence)

@@ -74,7 +74,7 @@ def make_runner(args, ops=None) -> ModelRunner:
         num_pages=max(1, tokens // page),
         max_seqs=MAX_LIVE,
         max_step_tokens=max(tokens, 1),
-        max_model_len=None,
+        max_model_len=max(tokens, 1),      # no request can outgrow the pool
         ops=ops,
         poison_pages=getattr(args, "poison_pages", False),
     )

@@ -19,8 +19,8 @@ class TorchOps:
 
     # ---------------------------------------------------------------- embedding and norms
 
-    def embed(self, token_ids, table, out, positions=None, position_table=None):
-        rows = table[token_ids.long()].to(self.acc)
+    def embed(self, token_ids, table, out, positions=None, position_table=None, scale=1.0):
+        rows = table[token_ids.long()].to(self.acc) * scale
         if position_table is not None:
             rows = rows + position_table[positions[:out.shape[0]].long()].to(self.acc)
         out.copy_(rows.to(out.dtype))
@@ -214,7 +214,7 @@ class TorchOps:
         self.paged_attention(qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale, window, out)
 
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale,
-                        window, out):
+                        window, out, sinks=None):
         group = num_heads // num_kv_heads
         q_start = batch.q_start.tolist()
         kv_lens = batch.kv_len.tolist()
@@ -240,7 +240,14 @@ class TorchOps:
             vals = vals.to(self.acc).repeat_interleave(group, dim=0)
             scores = torch.einsum("qhd,hkd->hqk", q, keys) * scale
             scores = scores.masked_fill(hidden[None], float("-inf"))
-            weights = torch.softmax(scores, dim=-1)
+            if sinks is None:
+                weights = torch.softmax(scores, dim=-1)
+            else:
+                # a sink is one more term of the denominator: no key, no value, not scaled
+                sink = sinks.to(self.acc)[:, None, None]
+                big = torch.maximum(scores.max(-1, keepdim=True).values, sink)
+                e = torch.exp(scores - big)
+                weights = e / (e.sum(-1, keepdim=True) + torch.exp(sink - big))
             weights = torch.nan_to_num(weights)  # a hidden key's value may be non-finite
             vals = torch.where(hidden.all(0)[None, :, None], torch.zeros_like(vals), vals)
             o = torch.einsum("hqk,hkd->qhd", weights, vals)
@@ -318,6 +325,181 @@ class TorchOps:
             vals = torch.where(hidden.all(0)[None, :, None], torch.zeros_like(vals), vals)
             o = torch.einsum("hqk,hkd->qhd", weights, vals)
             out[begin:end] = o.reshape(q_len, heads * vdim).to(out.dtype)
+
+    # ---------------------------------------------------------------- layer norm, scale, cap
+
+    def scaled_add_norm(self, h, delta, scale, weight, eps, center, out, rows=None):
+        """h += delta * scale (either may be None); then, if `weight` is given, out = norm(h)
+        * weight, a layer norm (`center`) or an RMS norm. With `rows` only those rows are
+        normalised and h is left as it was."""
+        add = None
+        if delta is not None:
+            add = delta.to(self.acc) * (scale.to(self.acc) if scale is not None else 1.0)
+        if rows is None:
+            if add is not None:
+                h.add_(add.to(h.dtype))
+            x = h.to(self.acc)
+        else:
+            index = rows.long()
+            x = h[index].to(self.acc)
+            if add is not None:
+                x = x + add[index]
+        if weight is None:
+            return
+        if center:
+            x = x - x.mean(-1, keepdim=True)
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+        out.copy_((x * weight.to(self.acc)).to(out.dtype))
+
+    def softcap(self, logits, cap):
+        logits.copy_((cap * torch.tanh(logits.to(self.acc) / cap)).to(logits.dtype))
+
+    # ---------------------------------------------------------------- state-space and delta rule
+
+    def conv_act(self, pre, offset, conv, bias, tail, batch, out, act):
+        """out[t] = act(sum_k conv[:, k] * x[t - (taps - 1 - k)] + bias), x = pre[:, offset:
+        offset + channels]; inputs before the step come from `tail` [slots, (taps - 1) *
+        channels] (input j tokens back at (j - 1) * channels), which is left as it was."""
+        channels, taps = conv.shape
+        for begin, end, slot in self._sequences(batch):
+            x = pre[begin:end, offset:offset + channels].to(self.acc)
+            past = tail[slot].to(self.acc).view(taps - 1, channels).flip(0)       # oldest first
+            padded = torch.cat([past, x])
+            acc = torch.zeros_like(x)
+            for k in range(taps):
+                acc = acc + padded[k:k + x.shape[0]] * conv[:, k].to(self.acc)
+            if bias is not None:
+                acc = acc + bias.to(self.acc)
+            if act == "silu":
+                acc = acc * torch.sigmoid(acc)
+            out[begin:end] = acc.to(out.dtype)
+
+    def conv_tail_update(self, pre, offset, channels, taps, tail, batch):
+        if taps <= 1:
+            return
+        for begin, end, slot in self._sequences(batch):
+            x = pre[begin:end, offset:offset + channels].to(tail.dtype)
+            old = tail[slot].view(taps - 1, channels).flip(0)
+            history = torch.cat([old, x])[-(taps - 1):]
+            tail[slot] = history.flip(0).reshape(-1)
+
+    def mamba2_scan(self, xbc, pre, dt_offset, dt_bias, neg_rate, skip, layout, cells, batch, y):
+        heads, vdim, n, groups = layout
+        inner, per = heads * vdim, heads // groups
+        for begin, end, slot in self._sequences(batch):
+            rows = xbc[begin:end].to(self.acc)
+            x = rows[:, :inner].view(-1, heads, vdim)
+            b = rows[:, inner:inner + groups * n].view(-1, groups, n).repeat_interleave(per, dim=1)
+            c = rows[:, inner + groups * n:].view(-1, groups, n).repeat_interleave(per, dim=1)
+            dt = torch.nn.functional.softplus(pre[begin:end, dt_offset:dt_offset + heads].to(self.acc)
+                                              + dt_bias.to(self.acc))
+            decay = torch.exp(neg_rate.to(self.acc) * dt)
+            s = cells[slot].to(self.acc).view(heads, n, vdim)
+            for t in range(end - begin):
+                s = decay[t, :, None, None] * s + dt[t, :, None, None] * b[t, :, :, None] * x[t, :, None, :]
+                out = torch.einsum("hnp,hn->hp", s, c[t]) + skip.to(self.acc)[:, None] * x[t]
+                y[begin + t] = out.reshape(-1).to(y.dtype)
+            cells[slot] = s.reshape(-1).to(cells.dtype)
+
+    def delta_rule_scan(self, qkv, pre, beta_offset, decay_offset, dt_bias, neg_rate, layout,
+                        unit_eps, cells, batch, o):
+        heads, key_heads, dim, vdim = layout
+        qk, per = key_heads * dim, heads // key_heads
+        for begin, end, slot in self._sequences(batch):
+            rows = qkv[begin:end].to(self.acc)
+            q = rows[:, :qk].view(-1, key_heads, dim)
+            k = rows[:, qk:2 * qk].view(-1, key_heads, dim)
+            v = rows[:, 2 * qk:].view(-1, heads, vdim)
+            q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + unit_eps) * dim ** -0.5
+            k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + unit_eps)
+            q, k = q.repeat_interleave(per, dim=1), k.repeat_interleave(per, dim=1)
+            beta = torch.sigmoid(pre[begin:end, beta_offset:beta_offset + heads].to(self.acc))
+            g = torch.exp(neg_rate.to(self.acc) * torch.nn.functional.softplus(
+                pre[begin:end, decay_offset:decay_offset + heads].to(self.acc) + dt_bias.to(self.acc)))
+            s = cells[slot].to(self.acc).view(heads, dim, vdim)
+            for t in range(end - begin):
+                s = g[t, :, None, None] * s
+                u = beta[t, :, None] * (v[t] - torch.einsum("hdp,hd->hp", s, k[t]))
+                s = s + k[t, :, :, None] * u[:, None, :]
+                o[begin + t] = torch.einsum("hdp,hd->hp", s, q[t]).reshape(-1).to(o.dtype)
+            cells[slot] = s.reshape(-1).to(cells.dtype)
+
+    def gated_group_norm(self, y, pre, gate_offset, weight, groups, eps, gate_first, out):
+        """RMS norm of y in `groups` equal parts, times `weight` (as long as a row, or as a
+        part and then shared by the parts), times silu(gate) before (`gate_first`) or behind
+        the norm; gate = pre[:, gate_offset : gate_offset + width]."""
+        tokens, width = y.shape
+        gate = pre[:, gate_offset:gate_offset + width].to(self.acc)
+        gate = gate * torch.sigmoid(gate)
+        x = y.to(self.acc)
+        if gate_first:
+            x = x * gate
+        x = x.view(tokens, groups, width // groups)
+        x = (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)).view(tokens, width)
+        x = x * weight.to(self.acc).repeat(width // weight.numel())
+        if not gate_first:
+            x = x * gate
+        out.copy_(x.to(out.dtype))
+
+    # ---------------------------------------------------------------- latent attention
+
+    def latent_norm_store(self, pre, offset, rank, weight, eps, batch, cache):
+        """c = rmsnorm(pre[:, offset : offset + rank]) * weight into the pages (one shared
+        head of size `rank`)."""
+        tokens = pre.shape[0]
+        x = pre[:, offset:offset + rank].to(self.acc)
+        c = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.to(self.acc)
+        live = batch.seq_of_token[:tokens] >= 0
+        pos = batch.positions[:tokens].long()
+        seq = batch.seq_of_token[:tokens].long().clamp(min=0)
+        page = cache.table[seq, pos // cache.page_size].long()
+        keep = live & (page >= 0)
+        cache.k[page[keep], 0, (pos % cache.page_size)[keep], :] = c[keep].to(cache.k.dtype)
+
+    def head_linear(self, x, offset, weight, out):
+        """out[t, h] = weight[h] x[t, h] with weight [heads, out, in] and x's heads side by
+        side from column `offset`."""
+        heads, _rows, cols = weight.shape
+        xs = x[:, offset:offset + heads * cols].to(self.acc).view(-1, heads, cols)
+        out.copy_(torch.einsum("hoi,thi->tho", weight.to(self.acc), xs).reshape(out.shape).to(out.dtype))
+
+    # ---------------------------------------------------------------- routed experts
+
+    def route_experts(self, x, router, correction, group_count, group_keep, route_scale, chosen,
+                      weights):
+        tokens, top = chosen.shape
+        experts = router.shape[0]
+        s = torch.sigmoid(self._x(x).to(self.acc) @ router.to(self.acc).T)
+        choice = s + correction.to(self.acc)
+        size = experts // group_count
+        grouped = choice.view(tokens, group_count, size)
+        score = grouped.topk(min(2, size), -1).values.sum(-1)
+        kept = score.topk(group_keep, -1).indices
+        allowed = torch.zeros(tokens, group_count, dtype=torch.bool, device=x.device)
+        allowed.scatter_(1, kept, True)
+        allowed = allowed[:, :, None].expand(-1, -1, size).reshape(tokens, experts)
+        index = choice.masked_fill(~allowed, float("-inf")).topk(top, -1).indices
+        chosen.copy_(index.to(chosen.dtype))
+        weights.copy_((s.gather(1, index) * route_scale).to(weights.dtype))
+
+    def expert_feed_forward(self, x, chosen, weights, gate_up, down, out, ctx=None):
+        """out[t] = sum_j weights[t, j] * down[e] (silu(gate[e] x[t]) * (up[e] x[t])), e =
+        chosen[t, j]; gate_up [experts, 2 ff, hidden] (gate rows first), down [experts,
+        hidden, ff]."""
+        x = self._x(x)
+        ff = down.shape[2]
+        total = torch.zeros(out.shape, dtype=self.acc, device=x.device)
+        for e in range(gate_up.shape[0]):
+            hit = (chosen == e)
+            rows = hit.any(-1).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            both = (x[rows].to(self.acc) @ gate_up[e].to(self.acc).T)
+            act = (both[:, :ff] * torch.sigmoid(both[:, :ff]) * both[:, ff:]).to(x.dtype).to(self.acc)
+            y = act @ down[e].to(self.acc).T
+            w = (weights[rows].to(self.acc) * hit[rows]).sum(-1, keepdim=True)
+            total[rows] += w * y
+        out.copy_(total.to(out.dtype))
 
     # ---------------------------------------------------------------- sampling
 

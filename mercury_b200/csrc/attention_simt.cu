@@ -33,7 +33,8 @@ paged_attention_kernel(const T* __restrict__ qkv, int q_row_stride, const T* __r
                        const int* __restrict__ q_start, const int* __restrict__ kv_len_of,
                        T* __restrict__ out, float* __restrict__ part_acc,
                        float* __restrict__ part_ml, int n_q, int n_kv, int d, int page_size,
-                       float scale, int window, int tiles_per_seq, int num_splits) {
+                       float scale, int window, int tiles_per_seq, int num_splits,
+                       const float* __restrict__ sinks) {
     grid_dependency_sync();
     extern __shared__ float smem[];
     const int seq = blockIdx.x / tiles_per_seq;
@@ -171,7 +172,10 @@ paged_attention_kernel(const T* __restrict__ qkv, int q_row_stride, const T* __r
         const int tok = row / group, hg = row - tok * group;
         const int64_t flat = (int64_t)(q_begin + tok) * n_q + kvh * group + hg;
         if (num_splits == 1) {
-            const float inv = l[rr] > 0.f ? 1.f / l[rr] : 0.f;
+            // a sink is one more term of the denominator: exp(sink) beside the keys' exp(score)
+            float denom = l[rr];
+            if (sinks && m[rr] > -INFINITY) denom += expf(sinks[kvh * group + hg] - m[rr]);
+            const float inv = denom > 0.f ? 1.f / denom : 0.f;
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
                 const int dim = lane + 32 * c;
@@ -197,7 +201,8 @@ template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
                                          const float* __restrict__ part_ml,
                                          const int* __restrict__ seq_of_token, T* __restrict__ out,
-                                         int n_q, int d, int num_splits) {
+                                         int n_q, int d, int num_splits,
+                                         const float* __restrict__ sinks) {
     grid_dependency_sync();
     const int tok = blockIdx.x, head = blockIdx.y;
     const int64_t flat = (int64_t)tok * n_q + head;
@@ -212,6 +217,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
         const float mz = part_ml[(flat * num_splits + z) * 2];
         if (mz > -INFINITY) denom += part_ml[(flat * num_splits + z) * 2 + 1] * expf(mz - big);
     }
+    if (sinks && big > -INFINITY) denom += expf(sinks[head] - big);
     const float inv = denom > 0.f ? 1.f / denom : 0.f;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float v = 0.f;
@@ -228,7 +234,7 @@ int launch_attention(const void* qkv, int q_row_stride, const void* k_pages, con
                      const int* table, int max_pages, const int* q_start, const int* kv_len,
                      void* out, float* part_acc, float* part_ml, int n_q, int n_kv, int d,
                      int page_size, float scale, int window, int num_seqs, int tiles_per_seq,
-                     int num_splits, cudaStream_t s) {
+                     int num_splits, const float* sinks, cudaStream_t s) {
     const size_t smem = (size_t)(ATT_ROWS * d + ATT_KEYS * (d + 1) + ATT_KEYS * d) * sizeof(float) +
                         ATT_KEYS * sizeof(int);
     static bool raised = false;  // one flag per instantiation
@@ -243,7 +249,7 @@ int launch_attention(const void* qkv, int q_row_stride, const void* k_pages, con
     MB_LAUNCH((paged_attention_kernel<T, NC>), grid, ATT_WARPS * 32, smem, s, 
         (const T*)qkv, q_row_stride, (const T*)k_pages, (const T*)v_pages, table, max_pages, q_start,
         kv_len, (T*)out, part_acc, part_ml, n_q, n_kv, d, page_size, scale, window, tiles_per_seq,
-        num_splits);
+        num_splits, sinks);
     return launch_status();
 }
 
@@ -252,13 +258,13 @@ int dispatch_attention(int nc, const void* qkv, int q_row_stride, const void* k_
                        const void* v_pages, const int* table, int max_pages, const int* q_start,
                        const int* kv_len, void* out, float* part_acc, float* part_ml, int n_q,
                        int n_kv, int d, int page_size, float scale, int window, int num_seqs,
-                       int tiles_per_seq, int num_splits, cudaStream_t s) {
+                       int tiles_per_seq, int num_splits, const float* sinks, cudaStream_t s) {
 #define MB_ATT_CASE(N)                                                                           \
     case N:                                                                                      \
         return launch_attention<T, N>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,     \
                                       q_start, kv_len, out, part_acc, part_ml, n_q, n_kv, d,     \
                                       page_size, scale, window, num_seqs, tiles_per_seq,         \
-                                      num_splits, s)
+                                      num_splits, sinks, s)
     switch (nc) {
         MB_ATT_CASE(1);
         MB_ATT_CASE(2);
@@ -277,15 +283,15 @@ int dispatch_attention(int nc, const void* qkv, int q_row_stride, const void* k_
 // attention kernel that splits keys. dtype: MB_F32 or MB_BF16 output.
 int launch_attention_combine(const float* part_acc, const float* part_ml, const int* seq_of_token,
                              void* out, int tokens, int n_q, int d, int num_splits, int dtype,
-                             cudaStream_t s) {
+                             cudaStream_t s, const float* sinks) {
     if (n_q > 65535) return MB_ERR_UNSUPPORTED_SIZE;
     dim3 grid(tokens, n_q);
     if (dtype == MB_F32)
         MB_LAUNCH((attention_combine_kernel<float>), grid, 64, 0, s, part_acc, part_ml, seq_of_token,
-                                                            (float*)out, n_q, d, num_splits);
+                                                            (float*)out, n_q, d, num_splits, sinks);
     else if (dtype == MB_BF16)
         MB_LAUNCH((attention_combine_kernel<__nv_bfloat16>), grid, 64, 0, s, 
-            part_acc, part_ml, seq_of_token, (__nv_bfloat16*)out, n_q, d, num_splits);
+            part_acc, part_ml, seq_of_token, (__nv_bfloat16*)out, n_q, d, num_splits, sinks);
     else
         return MB_ERR_BAD_DTYPE;
     return launch_status();
@@ -303,14 +309,16 @@ MB_EXPORT long long mb_attention_scratch_floats(int tokens, int n_q, int d, int 
 // max_q_len: the most query tokens one sequence has in this batch (sizes the grid).
 // scratch: float32 buffer of at least mb_attention_scratch_floats() (may be null when
 // num_splits is 1). Head sizes up to 256 are taken; anything else is refused.
-MB_EXPORT int mb_paged_attention_simt(const void* qkv, int q_row_stride, const void* k_pages,
-                                      const void* v_pages, const int* table, int max_pages,
-                                      const int* q_start, const int* kv_len,
-                                      const int* seq_of_token, void* out, float* scratch,
-                                      long long scratch_floats, int tokens, int num_seqs,
-                                      int max_q_len, int n_q, int n_kv, int d, int page_size,
-                                      float scale, int window, int num_splits, int dtype,
-                                      void* stream) {
+// `sinks`: null, or one float32 number per query head whose exponential joins the softmax's
+// denominator (it has no key and no value and is not scaled).
+MB_EXPORT int mb_paged_attention_simt_sinks(const void* qkv, int q_row_stride, const void* k_pages,
+                                            const void* v_pages, const int* table, int max_pages,
+                                            const int* q_start, const int* kv_len,
+                                            const int* seq_of_token, void* out, float* scratch,
+                                            long long scratch_floats, int tokens, int num_seqs,
+                                            int max_q_len, int n_q, int n_kv, int d, int page_size,
+                                            float scale, int window, int num_splits, int dtype,
+                                            const float* sinks, void* stream) {
     if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
     if (d <= 0 || d > 256 || n_kv <= 0 || n_q % n_kv) return MB_ERR_UNSUPPORTED_SIZE;
     if (page_size <= 0 || (page_size & (page_size - 1))) return MB_ERR_UNSUPPORTED_SIZE;
@@ -333,17 +341,31 @@ MB_EXPORT int mb_paged_attention_simt(const void* qkv, int q_row_stride, const v
         rc = dispatch_attention<float>(nc, qkv, q_row_stride, k_pages, v_pages, table, max_pages,
                                        q_start, kv_len, out, part_acc, part_ml, n_q, n_kv, d,
                                        page_size, scale, window, num_seqs, tiles_per_seq,
-                                       num_splits, s);
+                                       num_splits, sinks, s);
     else if (dtype == MB_BF16)
         rc = dispatch_attention<__nv_bfloat16>(nc, qkv, q_row_stride, k_pages, v_pages, table,
                                                max_pages, q_start, kv_len, out, part_acc, part_ml,
                                                n_q, n_kv, d, page_size, scale, window, num_seqs,
-                                               tiles_per_seq, num_splits, s);
+                                               tiles_per_seq, num_splits, sinks, s);
     else
         return MB_ERR_BAD_DTYPE;
     if (rc != MB_OK || num_splits == 1) return rc;
     return launch_attention_combine(part_acc, part_ml, seq_of_token, out, tokens, n_q, d,
-                                    num_splits, dtype, s);
+                                    num_splits, dtype, s, sinks);
+}
+
+MB_EXPORT int mb_paged_attention_simt(const void* qkv, int q_row_stride, const void* k_pages,
+                                      const void* v_pages, const int* table, int max_pages,
+                                      const int* q_start, const int* kv_len,
+                                      const int* seq_of_token, void* out, float* scratch,
+                                      long long scratch_floats, int tokens, int num_seqs,
+                                      int max_q_len, int n_q, int n_kv, int d, int page_size,
+                                      float scale, int window, int num_splits, int dtype,
+                                      void* stream) {
+    return mb_paged_attention_simt_sinks(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
+                                         q_start, kv_len, seq_of_token, out, scratch, scratch_floats,
+                                         tokens, num_seqs, max_q_len, n_q, n_kv, d, page_size, scale,
+                                         window, num_splits, dtype, nullptr, stream);
 }
 
 // ------------------------------------------------------------------------------------------

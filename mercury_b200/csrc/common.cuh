@@ -144,7 +144,7 @@ __device__ __forceinline__ int checked_position(int pos) {
 // defined in attention_simt.cu
 int launch_attention_combine(const float* part_acc, const float* part_ml, const int* seq_of_token,
                              void* out, int tokens, int n_q, int d, int num_splits, int dtype,
-                             cudaStream_t s);
+                             cudaStream_t s, const float* sinks = nullptr);
 
 // ---- programmatic dependent launch -----------------------------------------------------
 // Every kernel of this library starts with grid_dependency_sync(): when the launch carries

@@ -1,0 +1,358 @@
+// A feed-forward of routed experts: the router, the plan that sorts a step's (token, choice)
+// pairs by expert, the two grouped products and the weighted sum.
+//
+// Router (float32): s = sigmoid(Wr x); the choice is made on s + correction; the experts form
+// equal groups of neighbours, a group's score is the sum of its two largest choice scores,
+// only experts of the best `group_keep` groups can be chosen, and of those the `top` with
+// the largest choice scores are (ties: the lower index). A chosen expert's weight is
+// s * route_scale.
+//
+// Products: the pairs are sorted by expert and cut into tiles of EX_BM rows that belong to
+// one expert each, so that a block reads a tile of that expert's matrix once for all its
+// rows. The grid is sized for the most tiles a step of that many pairs can have; blocks
+// beyond the step's own count leave at once, so the launch sequence depends on the step's
+// shape only. Every output is one sum over k in ascending order, whatever else is in the
+// tile: a token's result does not depend on the batch. Each pair's result of the second
+// product is kept apart (float32) and a token's pairs are added in the order of the
+// router's choice.
+#include "common.cuh"
+
+namespace mb {
+
+constexpr int EX_BM = 32;   // rows (token, choice pairs) per tile
+constexpr int EX_BN = 64;   // output columns per block
+constexpr int EX_BK = 32;   // k per round
+
+// the better of two candidates: larger value, lower index on a tie; index -1 is no candidate
+__device__ __forceinline__ void take_better(float& v, int& i, float v2, int i2) {
+    if (i2 >= 0 && (i < 0 || v2 > v || (v2 == v && i2 < i))) {
+        v = v2;
+        i = i2;
+    }
+}
+
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v2 = __shfl_xor_sync(0xffffffffu, v, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, i, o);
+        take_better(v, i, v2, i2);
+    }
+}
+
+// A warp per token. Shared memory per warp: s[E], choice[E], group score[E], candidates[E].
+template <typename T>
+__global__ void route_experts_kernel(const T* __restrict__ x, const float* __restrict__ router,
+                                     const float* __restrict__ correction, int* __restrict__ chosen,
+                                     float* __restrict__ weights, int tokens, int hidden,
+                                     int experts, int top, int group_count, int group_keep,
+                                     float route_scale) {
+    grid_dependency_sync();
+    extern __shared__ float sm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= tokens) return;
+    float* s_s = sm + (size_t)warp * 4 * experts;
+    float* choice_s = s_s + experts;
+    float* group_s = choice_s + experts;
+    float* cand_s = group_s + experts;
+    const T* row = x + (int64_t)t * hidden;
+    for (int e = 0; e < experts; ++e) {
+        const float* wr = router + (int64_t)e * hidden;
+        float acc = 0.f;
+        for (int k = lane; k < hidden; k += 32) acc = fmaf(to_float(row[k]), wr[k], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            const float s = 1.f / (1.f + expf(-acc));
+            s_s[e] = s;
+            choice_s[e] = s + correction[e];
+        }
+    }
+    for (int e = lane; e < experts; e += 32) cand_s[e] = -INFINITY;
+    __syncwarp();
+    const int size = experts / group_count;
+    for (int g = lane; g < group_count; g += 32) {
+        float first = -INFINITY, second = -INFINITY;
+        for (int j = 0; j < size; ++j) {
+            const float v = choice_s[g * size + j];
+            if (v > first) {
+                second = first;
+                first = v;
+            } else if (v > second) {
+                second = v;
+            }
+        }
+        group_s[g] = size >= 2 ? first + second : first;
+    }
+    __syncwarp();
+    for (int round = 0; round < group_keep; ++round) {
+        float v = -INFINITY;
+        int i = -1;
+        for (int g = lane; g < group_count; g += 32)
+            if (group_s[g] > -INFINITY) take_better(v, i, group_s[g], g);
+        warp_argmax(v, i);
+        if (i < 0) break;                       // nothing comparable is left (a row of NaN)
+        for (int j = lane; j < size; j += 32) cand_s[i * size + j] = choice_s[i * size + j];
+        if (lane == 0) group_s[i] = -INFINITY;
+        __syncwarp();
+    }
+    for (int round = 0; round < top; ++round) {
+        float v = -INFINITY;
+        int i = -1;
+        for (int e = lane; e < experts; e += 32)
+            if (cand_s[e] > -INFINITY) take_better(v, i, cand_s[e], e);
+        warp_argmax(v, i);
+        if (lane == 0) {
+            // a row that is not a number chooses nothing: it gets an expert and no weight
+            chosen[(int64_t)t * top + round] = i >= 0 ? i : round % experts;
+            weights[(int64_t)t * top + round] = i >= 0 ? s_s[i] * route_scale : 0.f;
+            if (i >= 0) cand_s[i] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+// One block sorts the step's pairs by expert. plan: [0] tiles in all, then tile_expert[cap],
+// tile_row0[cap], tile_rows[cap], then perm[pairs] (pair = token * top + choice, grouped by
+// expert; the order inside an expert is arbitrary and changes no result).
+__global__ void __launch_bounds__(1024)
+expert_plan_kernel(const int* __restrict__ chosen, int pairs, int experts, int cap,
+                   int* __restrict__ plan) {
+    grid_dependency_sync();
+    extern __shared__ int ism[];
+    int* count_s = ism;                 // [experts]
+    int* start_s = ism + experts;       // [experts]
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) count_s[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = chosen[i];
+        if (e >= 0 && e < experts) atomicAdd(&count_s[e], 1);
+    }
+    __syncthreads();
+    int* tile_expert = plan + 1;
+    int* tile_row0 = tile_expert + cap;
+    int* tile_rows = tile_row0 + cap;
+    int* perm = tile_rows + cap;
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int e = 0; e < experts; ++e) {
+            start_s[e] = at;
+            for (int r = 0; r < count_s[e] && tiles < cap; r += EX_BM) {
+                tile_expert[tiles] = e;
+                tile_row0[tiles] = at + r;
+                tile_rows[tiles] = min(EX_BM, count_s[e] - r);
+                ++tiles;
+            }
+            at += count_s[e];
+        }
+        plan[0] = tiles;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = chosen[i];
+        if (e >= 0 && e < experts) perm[atomicAdd(&start_s[e], 1)] = i;
+    }
+}
+
+// MODE 0: rows of x gathered by pair (token = pair / top) times [gate rows; up rows] of the
+//         tile's expert, out = silu(gate) * up into act[sorted row][n] (type TA).
+// MODE 1: act[sorted row] times the expert's down matrix, into y[pair][n] (float32).
+// w: [experts][w_rows][K] with K contiguous (w_rows = 2 N in MODE 0, N in MODE 1).
+template <typename TA, typename TW, int MODE>
+__global__ void __launch_bounds__(256)
+expert_product_kernel(const TA* __restrict__ a, int a_ld, const TW* __restrict__ w,
+                      void* __restrict__ out, const int* __restrict__ plan, int cap, int top,
+                      int K, int N) {
+    grid_dependency_sync();
+    const int tile = blockIdx.x;
+    if (tile >= plan[0]) return;
+    const int* tile_expert = plan + 1;
+    const int* tile_row0 = tile_expert + cap;
+    const int* tile_rows = tile_row0 + cap;
+    const int* perm = tile_rows + cap;
+    const int e = tile_expert[tile], row0 = tile_row0[tile], rows = tile_rows[tile];
+    const int n0 = blockIdx.y * EX_BN;
+    constexpr int PARTS = MODE == 0 ? 2 : 1;
+    __shared__ float a_s[EX_BK][EX_BM + 1];
+    __shared__ __align__(16) float w_s[PARTS][EX_BK][EX_BN + 4];
+    __shared__ int src_s[EX_BM];
+    const int tid = threadIdx.x;
+    if (tid < EX_BM) {
+        int src = -1;
+        if (tid < rows) src = MODE == 0 ? perm[row0 + tid] / top : row0 + tid;
+        src_s[tid] = src;
+    }
+    __syncthreads();
+    const int ty = tid >> 4, tx = tid & 15;
+    float acc[PARTS][2][4];
+#pragma unroll
+    for (int p = 0; p < PARTS; ++p)
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[p][r][c] = 0.f;
+    const int w_rows = PARTS * N;
+    const TW* we = w + (int64_t)e * w_rows * K;
+    const int ar = tid >> 3, ak = (tid & 7) * 4;          // this thread's piece of the A tile
+    const int wn = tid >> 2, wk = (tid & 3) * 8;          // ... and of each W tile
+    for (int k0 = 0; k0 < K; k0 += EX_BK) {
+        {
+            const int src = src_s[ar];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int k = k0 + ak + j;
+                a_s[ak + j][ar] = (src >= 0 && k < K) ? to_float(a[(int64_t)src * a_ld + k]) : 0.f;
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < PARTS; ++p) {
+            const int n = n0 + wn;
+            const TW* wrow = we + (int64_t)(p * N + n) * K;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int k = k0 + wk + j;
+                w_s[p][wk + j][wn] = (n < N && k < K) ? to_float(wrow[k]) : 0.f;
+            }
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int k = 0; k < EX_BK; ++k) {
+            const float a0 = a_s[k][ty * 2], a1 = a_s[k][ty * 2 + 1];
+#pragma unroll
+            for (int p = 0; p < PARTS; ++p) {
+                const float4 wv = *reinterpret_cast<const float4*>(&w_s[p][k][tx * 4]);
+                acc[p][0][0] = fmaf(a0, wv.x, acc[p][0][0]);
+                acc[p][0][1] = fmaf(a0, wv.y, acc[p][0][1]);
+                acc[p][0][2] = fmaf(a0, wv.z, acc[p][0][2]);
+                acc[p][0][3] = fmaf(a0, wv.w, acc[p][0][3]);
+                acc[p][1][0] = fmaf(a1, wv.x, acc[p][1][0]);
+                acc[p][1][1] = fmaf(a1, wv.y, acc[p][1][1]);
+                acc[p][1][2] = fmaf(a1, wv.z, acc[p][1][2]);
+                acc[p][1][3] = fmaf(a1, wv.w, acc[p][1][3]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int lr = ty * 2 + r;
+        if (lr >= rows) continue;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int n = n0 + tx * 4 + c;
+            if (n >= N) continue;
+            if (MODE == 0) {
+                const float g = acc[0][r][c], u = acc[PARTS - 1][r][c];
+                reinterpret_cast<TA*>(out)[(int64_t)(row0 + lr) * N + n] =
+                    from_float<TA>(g / (1.f + expf(-g)) * u);
+            } else {
+                reinterpret_cast<float*>(out)[(int64_t)perm[row0 + lr] * N + n] = acc[0][r][c];
+            }
+        }
+    }
+}
+
+// out[t][n] = sum_j weights[t][j] * y[t * top + j][n], j ascending.
+__global__ void expert_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
+                                      float* __restrict__ out, int tokens, int top, int hidden) {
+    grid_dependency_sync();
+    const int64_t total = (int64_t)tokens * hidden;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / hidden;
+        const int n = (int)(i - t * hidden);
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j)
+            acc = fmaf(weights[t * top + j], y[(t * top + j) * hidden + n], acc);
+        out[i] = acc;
+    }
+}
+
+template <typename TA, typename TW>
+int launch_expert_product(int mode, const void* a, int a_ld, const void* w, void* out,
+                          const int* plan, int cap, int top, int K, int N, cudaStream_t s) {
+    dim3 grid(cap, (N + EX_BN - 1) / EX_BN);
+    if (grid.y > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    if (mode == 0)
+        MB_LAUNCH((expert_product_kernel<TA, TW, 0>), grid, 256, 0, s, (const TA*)a, a_ld, (const TW*)w,
+                  out, plan, cap, top, K, N);
+    else
+        MB_LAUNCH((expert_product_kernel<TA, TW, 1>), grid, 256, 0, s, (const TA*)a, a_ld, (const TW*)w,
+                  out, plan, cap, top, K, N);
+    return launch_status();
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+// x_dtype: the activations' type; router and correction are float32.
+MB_EXPORT int mb_route_experts(const void* x, int x_dtype, const float* router,
+                               const float* correction, int* chosen, float* weights, int tokens,
+                               int hidden, int experts, int top, int group_count, int group_keep,
+                               float route_scale, void* stream) {
+    if (tokens <= 0) return MB_OK;
+    if (experts <= 0 || top <= 0 || top > experts || group_count <= 0 || experts % group_count ||
+        group_keep <= 0 || group_keep > group_count)
+        return MB_ERR_UNSUPPORTED_SIZE;
+    int warps = 4;
+    while (warps > 1 && (size_t)warps * 4 * experts * sizeof(float) > 40 * 1024) warps >>= 1;
+    const size_t smem = (size_t)warps * 4 * experts * sizeof(float);
+    if (smem > 40 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
+    const int blocks = (tokens + warps - 1) / warps;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (x_dtype == MB_F32)
+        MB_LAUNCH((route_experts_kernel<float>), blocks, warps * 32, smem, s, (const float*)x, router,
+                  correction, chosen, weights, tokens, hidden, experts, top, group_count, group_keep,
+                  route_scale);
+    else if (x_dtype == MB_BF16)
+        MB_LAUNCH((route_experts_kernel<__nv_bfloat16>), blocks, warps * 32, smem, s,
+                  (const __nv_bfloat16*)x, router, correction, chosen, weights, tokens, hidden, experts,
+                  top, group_count, group_keep, route_scale);
+    else
+        return MB_ERR_BAD_DTYPE;
+    return launch_status();
+}
+
+// The most tiles a step of `pairs` pairs over `experts` experts can have.
+MB_EXPORT int mb_expert_tile_cap(int pairs, int experts) {
+    const int bound = pairs / EX_BM + experts;
+    return pairs < bound ? pairs : bound;
+}
+
+// Integers the plan needs: 1 + 3 * cap + pairs.
+MB_EXPORT int mb_expert_plan(const int* chosen, int pairs, int experts, int cap, int* plan,
+                             void* stream) {
+    if (pairs <= 0) return MB_OK;
+    if (experts <= 0 || experts > 4096 || cap <= 0) return MB_ERR_UNSUPPORTED_SIZE;
+    MB_LAUNCH((expert_plan_kernel), 1, 1024, (size_t)2 * experts * sizeof(int), (cudaStream_t)stream,
+              chosen, pairs, experts, cap, plan);
+    return launch_status();
+}
+
+// mode 0: gate/up with the SiLU gate (a = the tokens' rows, out = act in the activations'
+// type); mode 1: down (a = act, out = float32 rows per pair). dtype: of a and w alike.
+MB_EXPORT int mb_expert_product(int mode, const void* a, int a_ld, const void* w, void* out,
+                                const int* plan, int cap, int top, int K, int N, int dtype,
+                                void* stream) {
+    if (cap <= 0) return MB_OK;
+    if (K <= 0 || N <= 0 || (mode != 0 && mode != 1)) return MB_ERR_UNSUPPORTED_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MB_F32)
+        return launch_expert_product<float, float>(mode, a, a_ld, w, out, plan, cap, top, K, N, s);
+    if (dtype == MB_BF16)
+        return launch_expert_product<__nv_bfloat16, __nv_bfloat16>(mode, a, a_ld, w, out, plan, cap, top,
+                                                                   K, N, s);
+    return MB_ERR_BAD_DTYPE;
+}
+
+MB_EXPORT int mb_expert_combine(const float* y, const float* weights, float* out, int tokens,
+                                int top, int hidden, void* stream) {
+    const long long total = (long long)tokens * hidden;
+    if (total <= 0) return MB_OK;
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+    MB_LAUNCH((expert_combine_kernel), blocks, 256, 0, (cudaStream_t)stream, y, weights, out, tokens,
+              top, hidden);
+    return launch_status();
+}

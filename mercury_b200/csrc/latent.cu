@@ -1,0 +1,148 @@
+// Attention over a cached latent: what stands around the attention kernel itself.
+//
+// The cache keeps one row c of `rank` numbers per token. A head's key is Wuk_h c and its
+// value Wuv_h c, so q_h . k_h = (Wuk_h^T q_h) . c: the query is taken into the latent space
+// once per token (`head_linear` with the transposed up-projection), the attention kernel
+// then runs all heads over the cached rows as one shared key/value head of size `rank`, and
+// `head_linear` applies Wuv_h to each head's weighted sum of rows.
+#include "common.cuh"
+
+namespace mb {
+
+// c = x / sqrt(mean(x^2) + eps) * w for x = pre[t][offset .. offset + rank), stored into the
+// token's slot of the pages [page][1][slot][rank]. A warp per token; float32 arithmetic.
+template <typename T>
+__global__ void latent_norm_store_kernel(const float* __restrict__ pre, int ld, int offset,
+                                         const void* __restrict__ w, int w_dtype, float eps,
+                                         const int* __restrict__ positions,
+                                         const int* __restrict__ seq_of_token,
+                                         const int* __restrict__ table, int max_pages,
+                                         T* __restrict__ pages, int rank, int page_size,
+                                         int tokens) {
+    grid_dependency_sync();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= tokens) return;
+    const int seq = seq_of_token[t];
+    if (seq < 0) return;
+    const int pos = positions[t];
+    const int page = table_page(table, seq, max_pages, pos / page_size);
+    if (page < 0) return;
+    const float* x = pre + (int64_t)t * ld + offset;
+    float ss = 0.f;
+    for (int c = lane; c < rank; c += 32) ss = fmaf(x[c], x[c], ss);
+    ss = warp_sum(ss);
+    const float rstd = 1.f / sqrtf(ss / (float)rank + eps);
+    T* row = pages + ((int64_t)page * page_size + (pos % page_size)) * rank;
+    for (int c = lane; c < rank; c += 32)
+        row[c] = from_float<T>(x[c] * rstd * load_as_float(w, c, w_dtype));
+}
+
+// out[t][h][o] = sum_i w[h][i][o] * x[t][offset + h * in + i]: one small matrix per head, held
+// input-major so that consecutive threads (outputs o) read consecutive addresses. A block
+// computes 128 outputs of one head for HL_TOKENS tokens, the inputs staged token-minor; i
+// ascends, so the order of each sum is fixed. Sums are float32.
+template <typename TX, typename TW, typename TO, int HL_TOKENS>
+__global__ void __launch_bounds__(128)
+head_linear_kernel(const TX* __restrict__ x, int ld, int offset, const TW* __restrict__ w,
+                   TO* __restrict__ out, int tokens, int heads, int in, int outs) {
+    grid_dependency_sync();
+    extern __shared__ __align__(16) float x_s[];          // [in][HL_TOKENS]
+    const int per = (outs + 127) / 128;
+    const int otile = blockIdx.x % per;
+    const int h = blockIdx.x / per;
+    const int t0 = blockIdx.y * HL_TOKENS;
+    for (int idx = threadIdx.x; idx < HL_TOKENS * in; idx += blockDim.x) {
+        const int tt = idx / in, i = idx - tt * in;
+        x_s[i * HL_TOKENS + tt] =
+            t0 + tt < tokens ? to_float(x[(int64_t)(t0 + tt) * ld + offset + h * in + i]) : 0.f;
+    }
+    __syncthreads();
+    const int o = otile * 128 + threadIdx.x;
+    if (o >= outs) return;
+    const TW* wh = w + (int64_t)h * in * outs + o;
+    float acc[HL_TOKENS];
+#pragma unroll
+    for (int tt = 0; tt < HL_TOKENS; ++tt) acc[tt] = 0.f;
+#pragma unroll 4
+    for (int i = 0; i < in; ++i) {
+        const float v = to_float(wh[(int64_t)i * outs]);
+        const float4* row = reinterpret_cast<const float4*>(x_s + i * HL_TOKENS);
+#pragma unroll
+        for (int q = 0; q < HL_TOKENS / 4; ++q) {
+            const float4 xv = row[q];
+            acc[4 * q] = fmaf(v, xv.x, acc[4 * q]);
+            acc[4 * q + 1] = fmaf(v, xv.y, acc[4 * q + 1]);
+            acc[4 * q + 2] = fmaf(v, xv.z, acc[4 * q + 2]);
+            acc[4 * q + 3] = fmaf(v, xv.w, acc[4 * q + 3]);
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < HL_TOKENS; ++tt)
+        if (t0 + tt < tokens)
+            out[(int64_t)(t0 + tt) * heads * outs + h * outs + o] = from_float<TO>(acc[tt]);
+}
+
+template <typename TX, typename TW, typename TO>
+int launch_head_linear(const void* x, int ld, int offset, const void* w, void* out, int tokens,
+                       int heads, int in, int outs, cudaStream_t s) {
+    const bool few = tokens <= 8;
+    const int tile = few ? 4 : 16;
+    const size_t smem = (size_t)tile * in * sizeof(float);
+    if (smem > 48 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
+    const int rows = (tokens + tile - 1) / tile;
+    if (rows > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    dim3 grid(((outs + 127) / 128) * heads, rows);
+    if (few)
+        MB_LAUNCH((head_linear_kernel<TX, TW, TO, 4>), grid, 128, smem, s, (const TX*)x, ld, offset,
+                  (const TW*)w, (TO*)out, tokens, heads, in, outs);
+    else
+        MB_LAUNCH((head_linear_kernel<TX, TW, TO, 16>), grid, 128, smem, s, (const TX*)x, ld, offset,
+                  (const TW*)w, (TO*)out, tokens, heads, in, outs);
+    return launch_status();
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+// dtype: the pages' type (MB_F32 or MB_BF16); w_dtype: the norm weight's.
+MB_EXPORT int mb_latent_norm_store(const float* pre, int ld, int offset, const void* w, int w_dtype,
+                                   float eps, const int* positions, const int* seq_of_token,
+                                   const int* table, int max_pages, void* pages, int rank,
+                                   int page_size, int tokens, int dtype, void* stream) {
+    if (tokens <= 0 || rank <= 0) return MB_OK;
+    if (page_size <= 0) return MB_ERR_UNSUPPORTED_SIZE;
+    const int blocks = (tokens + 3) / 4;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MB_F32)
+        MB_LAUNCH((latent_norm_store_kernel<float>), blocks, 128, 0, s, pre, ld, offset, w, w_dtype, eps,
+                  positions, seq_of_token, table, max_pages, (float*)pages, rank, page_size, tokens);
+    else if (dtype == MB_BF16)
+        MB_LAUNCH((latent_norm_store_kernel<__nv_bfloat16>), blocks, 128, 0, s, pre, ld, offset, w,
+                  w_dtype, eps, positions, seq_of_token, table, max_pages, (__nv_bfloat16*)pages, rank,
+                  page_size, tokens);
+    else
+        return MB_ERR_BAD_DTYPE;
+    return launch_status();
+}
+
+// x [tokens][ld] (its heads from column `offset`), w [heads][in][outs], out [tokens][heads *
+// outs]; each of the three float32 or bfloat16.
+MB_EXPORT int mb_head_linear(const void* x, int x_dtype, int ld, int offset, const void* w,
+                             int w_dtype, void* out, int out_dtype, int tokens, int heads, int in,
+                             int outs, void* stream) {
+    if (tokens <= 0 || heads <= 0) return MB_OK;
+    if (in <= 0 || outs <= 0) return MB_ERR_UNSUPPORTED_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    typedef __nv_bfloat16 bf;
+    const int key = x_dtype * 4 + w_dtype * 2 + out_dtype;
+    switch (key) {
+        case 0: return launch_head_linear<float, float, float>(x, ld, offset, w, out, tokens, heads, in, outs, s);
+        case 3: return launch_head_linear<float, bf, bf>(x, ld, offset, w, out, tokens, heads, in, outs, s);
+        case 7: return launch_head_linear<bf, bf, bf>(x, ld, offset, w, out, tokens, heads, in, outs, s);
+        case 2: return launch_head_linear<float, bf, float>(x, ld, offset, w, out, tokens, heads, in, outs, s);
+        case 1: return launch_head_linear<float, float, bf>(x, ld, offset, w, out, tokens, heads, in, outs, s);
+    }
+    return MB_ERR_BAD_DTYPE;
+}

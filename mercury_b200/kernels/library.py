@@ -98,6 +98,37 @@ _SIGNATURES = {
     "mb_block_gates": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "mb_gated_recurrence_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_paged_attention_simt_sinks": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
+                                      c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
+                                      c_void_p, c_void_p],
+    "mb_embed_scaled": [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    "mb_scaled_add_norm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_int,
+                           c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+    "mb_softcap": [c_void_p, c_longlong, c_float, c_void_p],
+    "mb_conv_act": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_conv_tail_update": [c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
+                            c_int, c_int, c_void_p],
+    "mb_mamba2_scan": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                       c_void_p],
+    "mb_delta_rule_scan": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                           c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                           c_int, c_int, c_void_p],
+    "mb_gated_group_norm": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float,
+                            c_int, c_void_p, c_int, c_int, c_void_p],
+    "mb_latent_norm_store": [c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p,
+                             c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_head_linear": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                       c_int, c_int, c_void_p],
+    "mb_route_experts": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                         c_int, c_int, c_int, c_float, c_void_p],
+    "mb_expert_tile_cap": [c_int, c_int],
+    "mb_expert_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "mb_expert_product": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                          c_int, c_int, c_void_p],
+    "mb_expert_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "mb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }

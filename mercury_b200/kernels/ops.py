@@ -251,10 +251,17 @@ class CudaOps:
     # ------------------------------------------------------------------ kernels
 
     @_timed("embedding")
-    def embed(self, token_ids, table, out, positions=None, position_table=None):
-        """out = table[token_ids] (+ position_table[positions]) in the float32 stream."""
+    def embed(self, token_ids, table, out, positions=None, position_table=None, scale=1.0):
+        """out = table[token_ids] (+ position_table[positions]) in the float32 stream; with
+        `scale` (and no positions) every row is multiplied by it."""
         self._rows(out)
-        if position_table is None:
+        if scale != 1.0:
+            if position_table is not None:
+                raise KernelError("embed: a scale together with learned positions is not built")
+            check(self.lib.mb_embed_scaled(_ptr(token_ids), _ptr(table), _flag(table.dtype),
+                                           float(scale), _ptr(out), out.shape[0], out.shape[1],
+                                           table.shape[0], self._stream()), "embed")
+        elif position_table is None:
             check(self.lib.mb_embed(_ptr(token_ids), _ptr(table), _flag(table.dtype), _ptr(out),
                                     out.shape[0], out.shape[1], table.shape[0], self._stream()),
                   "embed")
@@ -583,6 +590,167 @@ class CudaOps:
             out.shape[1], state.shape[1], _flag(out.dtype), self._stream()), "gated_recurrence_scan")
         self.launches += 1
 
+    # ------------------------------------------------------------------ stream, layer scale, cap
+
+    @_timed("norm")
+    def scaled_add_norm(self, h, delta, scale, weight, eps, center, out, rows=None):
+        """h += delta * scale (either may be None); then, if `weight` is given, out = the
+        layer norm (`center`) or RMS norm of the new rows times weight. With `rows` only
+        those rows are normalised and h is left as it was."""
+        self._rows(h)
+        count = h.shape[0] if rows is None else rows.shape[0]
+        if delta is not None:
+            self._rows(delta)
+        check(self.lib.mb_scaled_add_norm(
+            _ptr(h), _ptr(delta), _flag(delta.dtype) if delta is not None else 0, _ptr(scale),
+            _flag(scale.dtype) if scale is not None else 0, _ptr(weight),
+            _flag(weight.dtype) if weight is not None else 0, float(eps), int(bool(center)),
+            _ptr(out) if weight is not None else None,
+            _flag(out.dtype) if (weight is not None and out is not None) else 0, _ptr(rows), count,
+            h.shape[1], self._stream()), "scaled_add_norm")
+        self.launches += 1
+        if rows is None and delta is not None:
+            self._note_stream_write()
+
+    @_timed("head")
+    def softcap(self, logits, cap):
+        """logits <- cap * tanh(logits / cap), in place (float32)."""
+        self._rows(logits)
+        check(self.lib.mb_softcap(_ptr(logits), logits.numel(), float(cap), self._stream()), "softcap")
+        self.launches += 1
+
+    # ------------------------------------------------------------------ state-space, delta rule
+
+    @_timed("recurrence")
+    def conv_act(self, pre, offset, conv, bias, tail, batch, out, act):
+        """out = act(causal convolution per channel of pre[:, offset : offset + channels] +
+        bias), float32; `tail` [slots, (taps - 1) * channels] (a view of the state rows) holds
+        the inputs from before the step and is left as it was. act: "silu" or None."""
+        channels, taps = conv.shape
+        if act not in ("silu", None):
+            raise KernelError(f"conv_act: no activation {act!r}")
+        check(self.lib.mb_conv_act(
+            _ptr(pre), pre.shape[1], int(offset), _ptr(conv), _ptr(bias), _ptr(tail), tail.stride(0),
+            _ptr(batch.q_start), _ptr(batch.slots), _ptr(batch.seq_of_token), _ptr(out), out.shape[0],
+            channels, taps, 1 if act == "silu" else 0, self._stream()), "conv_act")
+        self.launches += 1
+
+    @_timed("recurrence")
+    def conv_tail_update(self, pre, offset, channels, taps, tail, batch):
+        """Bring the convolution's past inputs up to the end of the step."""
+        if taps <= 1:
+            return
+        check(self.lib.mb_conv_tail_update(
+            _ptr(pre), pre.shape[1], int(offset), _ptr(tail), tail.stride(0), _ptr(batch.q_start),
+            _ptr(batch.slots), batch.num_seqs, int(channels), int(taps), self._stream()),
+            "conv_tail_update")
+        self.launches += 1
+
+    @_timed("recurrence")
+    def mamba2_scan(self, xbc, pre, dt_offset, dt_bias, neg_rate, skip, layout, cells, batch, y):
+        """S <- exp(neg_rate dt) S + dt B x^T, y = S^T C + skip x per head, dt = softplus(pre[:,
+        dt_offset + head] + dt_bias); xbc = [x | B | C]; `cells` [slots, heads * state * vdim]
+        is a view of the state rows; everything float32."""
+        heads, vdim, n_state, groups = layout
+        check(self.lib.mb_mamba2_scan(
+            _ptr(xbc), _ptr(pre), pre.shape[1], int(dt_offset), _ptr(dt_bias), _ptr(neg_rate),
+            _ptr(skip), _ptr(cells), cells.stride(0), _ptr(batch.q_start), _ptr(batch.slots), _ptr(y),
+            batch.num_seqs, heads, vdim, n_state, groups, self._stream()), "mamba2_scan")
+        self.launches += 1
+
+    @_timed("recurrence")
+    def delta_rule_scan(self, qkv, pre, beta_offset, decay_offset, dt_bias, neg_rate, layout,
+                        unit_eps, cells, batch, o):
+        """The gated delta rule per head over qkv = [q | k | v]; beta and the decay are read
+        off pre[:, beta_offset + head] and pre[:, decay_offset + head]; `cells` [slots, heads *
+        dim * vdim] is a view of the state rows; everything float32."""
+        heads, key_heads, dim, vdim = layout
+        check(self.lib.mb_delta_rule_scan(
+            _ptr(qkv), _ptr(pre), pre.shape[1], int(beta_offset), int(decay_offset), _ptr(dt_bias),
+            _ptr(neg_rate), float(unit_eps), _ptr(cells), cells.stride(0), _ptr(batch.q_start),
+            _ptr(batch.slots), _ptr(o), batch.num_seqs, heads, key_heads, dim, vdim, self._stream()),
+            "delta_rule_scan")
+        self.launches += 1
+
+    @_timed("recurrence")
+    def gated_group_norm(self, y, pre, gate_offset, weight, groups, eps, gate_first, out):
+        """RMS norm of y (float32) in `groups` equal parts times `weight` (read at c modulo its
+        length), times silu(pre[:, gate_offset + c]) before (`gate_first`) or behind the norm."""
+        tokens, width = y.shape
+        check(self.lib.mb_gated_group_norm(
+            _ptr(y), _ptr(pre), pre.shape[1], int(gate_offset), _ptr(weight), weight.numel(),
+            int(groups), width // int(groups), float(eps), int(bool(gate_first)), _ptr(out),
+            _flag(out.dtype), tokens, self._stream()), "gated_group_norm")
+        self.launches += 1
+
+    # ------------------------------------------------------------------ latent attention
+
+    @_timed("rotary + store")
+    def latent_norm_store(self, pre, offset, rank, weight, eps, batch, cache):
+        """c = rmsnorm(pre[:, offset : offset + rank]) * weight into the pages (one shared head
+        of size `rank`)."""
+        self._check_limits(cache)
+        check(self.lib.mb_latent_norm_store(
+            _ptr(pre), pre.shape[1], int(offset), _ptr(weight), _flag(weight.dtype), float(eps),
+            _ptr(batch.positions), _ptr(batch.seq_of_token), _ptr(cache.table), cache.table.shape[1],
+            _ptr(cache.k), int(rank), cache.page_size, pre.shape[0], _flag(cache.k.dtype),
+            self._stream()), "latent_norm_store")
+        self.launches += 1
+
+    @_timed("head product")
+    def head_linear(self, x, offset, weight, out):
+        """out[t, h] = weight[h]^T x[t, h]: weight [heads, in, out] (input-major), x's heads
+        side by side from column `offset`."""
+        heads, cols, outs = weight.shape
+        self._rows(weight)
+        check(self.lib.mb_head_linear(
+            _ptr(x), _flag(x.dtype), x.shape[1], int(offset), _ptr(weight), _flag(weight.dtype),
+            _ptr(out), _flag(out.dtype), x.shape[0], heads, cols, outs, self._stream()), "head_linear")
+        self.launches += 1
+
+    # ------------------------------------------------------------------ routed experts
+
+    @_timed("router")
+    def route_experts(self, x, router, correction, group_count, group_keep, route_scale, chosen,
+                      weights):
+        if self._pending(x) is not None:
+            x = x.materialize()
+        tokens, top = chosen.shape
+        check(self.lib.mb_route_experts(
+            _ptr(x), _flag(x.dtype), _ptr(router), _ptr(correction), _ptr(chosen), _ptr(weights),
+            tokens, x.shape[1], router.shape[0], top, int(group_count), int(group_keep),
+            float(route_scale), self._stream()), "route_experts")
+        self.launches += 1
+
+    @_timed("expert products")
+    def expert_feed_forward(self, x, chosen, weights, gate_up, down, out, ctx):
+        """out[t] = sum_j weights[t, j] * down[e] (silu(gate[e] x[t]) * (up[e] x[t])), e =
+        chosen[t, j]: the step's (token, choice) pairs sorted by expert, two grouped products,
+        and the weighted sum in the order of the choice."""
+        if self._pending(x) is not None:
+            x = x.materialize()
+        tokens, top = chosen.shape
+        experts, _two_ff, hidden = gate_up.shape
+        ff = down.shape[2]
+        pairs = tokens * top
+        cap = self.lib.mb_expert_tile_cap(pairs, experts)
+        plan = ctx.buffer("expert_plan", 1 + 3 * cap + pairs, 1, dtype=torch.int32)
+        check(self.lib.mb_expert_plan(_ptr(chosen), pairs, experts, cap, _ptr(plan), self._stream()),
+              "expert_plan")
+        act = ctx.buffer("expert_act", pairs, ff)
+        if act.dtype != x.dtype or gate_up.dtype != x.dtype or down.dtype != x.dtype:
+            raise KernelError("expert_feed_forward: activations and expert matrices differ in dtype")
+        check(self.lib.mb_expert_product(0, _ptr(x), x.shape[1], _ptr(gate_up), _ptr(act), _ptr(plan),
+                                         cap, top, hidden, ff, _flag(x.dtype), self._stream()),
+              "expert gate/up product")
+        y = ctx.buffer("expert_rows", pairs, hidden, dtype="float32")
+        check(self.lib.mb_expert_product(1, _ptr(act), ff, _ptr(down), _ptr(y), _ptr(plan), cap, top,
+                                         ff, hidden, _flag(x.dtype), self._stream()),
+              "expert down product")
+        check(self.lib.mb_expert_combine(_ptr(y), _ptr(weights), _ptr(out), tokens, top, hidden,
+                                         self._stream()), "expert_combine")
+        self.launches += 4
+
     # ------------------------------------------------------------------ mixed-head attention
 
     @_timed("rotary + store")
@@ -778,12 +946,16 @@ class CudaOps:
 
     @_timed("attention")
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale,
-                        window, out, kernel: str | None = None):
+                        window, out, kernel: str | None = None, sinks=None):
         """`kernel` forces "mma" or "simt"; by default bfloat16 with a head size the
-        tensor-core kernel takes runs there, everything else on the CUDA cores."""
+        tensor-core kernel takes runs there, everything else on the CUDA cores. `sinks`
+        (float32, one per query head): exp(sink) joins the softmax's denominator."""
         group = num_heads // num_kv_heads
         tokens = qkv.shape[0]
         self._check_limits(cache)
+        if sinks is not None:
+            return self._attention_with_sinks(qkv, num_heads, num_kv_heads, head_dim, batch, cache,
+                                              scale, window, out, sinks)
         tc_ok = (qkv.dtype == torch.bfloat16 and self.lib.mb_attention_tcgen05_supports(
             head_dim, cache.page_size, num_heads, num_kv_heads, qkv.shape[1]))
         if kernel == "tcgen05" and not tc_ok:
@@ -839,6 +1011,22 @@ class CudaOps:
         else:
             check(self.lib.mb_paged_attention_simt(*common, _flag(qkv.dtype), self._stream()),
                   "paged_attention")
+        self.launches += 1 if splits == 1 else 2
+
+    def _attention_with_sinks(self, qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale,
+                              window, out, sinks):
+        group = num_heads // num_kv_heads
+        tokens = qkv.shape[0]
+        splits = self._splits(batch, num_kv_heads, group, 16, 32)
+        floats = self.lib.mb_attention_scratch_floats(tokens, num_heads, head_dim, splits)
+        scratch = self._scratch_for(floats) if floats else None
+        check(self.lib.mb_paged_attention_simt_sinks(
+            _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
+            cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(batch.seq_of_token),
+            _ptr(out), _ptr(scratch), scratch.numel() if scratch is not None else 0, tokens,
+            batch.num_seqs, batch.max_q_len, num_heads, num_kv_heads, head_dim, cache.page_size,
+            float(scale), int(window), splits, _flag(qkv.dtype), _ptr(sinks), self._stream()),
+            "paged_attention (sinks)")
         self.launches += 1 if splits == 1 else 2
 
     @_timed("attention")

@@ -293,9 +293,11 @@ class LatentAttention(Mixer):
         widest = torch.float32 if any(t.dtype == torch.float32 for t in mats) else mats[0].dtype
         self.in_weight = torch.cat([t.to(widest) for t in mats], dim=0).contiguous()   # rows [q; dkv]
         up_k = setup.place(tensors[p + n["up_k"]])
-        # per head [rank, dim]: the transposed up-projection, which takes a query to the latent
-        self.absorb = up_k.view(self.num_heads, self.head_dim, self.rank).transpose(1, 2).contiguous()
-        self.up_v = setup.place(tensors[p + n["up_v"]]).view(self.num_heads, self.value_dim, self.rank)
+        # both per head and input-major, [heads, in, out]: the key up-projection as stored is the
+        # map that takes a query to the latent (its transpose); the value up-projection is turned
+        self.absorb = up_k.view(self.num_heads, self.head_dim, self.rank).contiguous()
+        self.up_v = (setup.place(tensors[p + n["up_v"]]).view(self.num_heads, self.value_dim, self.rank)
+                     .transpose(1, 2).contiguous())
         self.sink = setup.place(tensors[p + n["sink"]]).float().contiguous()
         self.out_weight = setup.place(tensors[p + n["o"]])
 

@@ -457,11 +457,11 @@ class TorchOps:
         cache.k[page[keep], 0, (pos % cache.page_size)[keep], :] = c[keep].to(cache.k.dtype)
 
     def head_linear(self, x, offset, weight, out):
-        """out[t, h] = weight[h] x[t, h] with weight [heads, out, in] and x's heads side by
-        side from column `offset`."""
-        heads, _rows, cols = weight.shape
-        xs = x[:, offset:offset + heads * cols].to(self.acc).view(-1, heads, cols)
-        out.copy_(torch.einsum("hoi,thi->tho", weight.to(self.acc), xs).reshape(out.shape).to(out.dtype))
+        """out[t, h] = weight[h]^T x[t, h] with weight [heads, in, out] (input-major) and x's
+        heads side by side from column `offset`."""
+        heads, cols, _outs = weight.shape
+        xs = x[:, offset:offset + heads * cols].to(self.acc).reshape(-1, heads, cols)
+        out.copy_(torch.einsum("hio,thi->tho", weight.to(self.acc), xs).reshape(out.shape).to(out.dtype))
 
     # ---------------------------------------------------------------- routed experts
 

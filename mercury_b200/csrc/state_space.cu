@@ -14,6 +14,16 @@
 // tokens' inputs are staged through shared memory sixteen tokens at a time, so the block
 // meets once per sixteen tokens. A column's arithmetic is the same however the tokens were
 // cut into steps.
+//
+// The template parameter S is the type the matrix is held in while a step runs. A float32
+// matrix that takes in a thousand tokens one by one gathers a rounding error of some 1e-6 of
+// its size, which is small beside bfloat16 activations and is what the bfloat16 engine runs
+// with; the float32 engine holds the matrix and its sums in double inside a step (S =
+// double) and rounds to float32 only when the step's last token is in, so a long prompt
+// costs one rounding where it would cost one per token. The decay that multiplies the matrix
+// at every token is computed in double in both and rounded once: an error of an ulp in expf
+// that leans one way grows linearly with the number of tokens a contribution has to survive.
+// Between steps the state is float32 in both.
 #include "common.cuh"
 
 namespace mb {
@@ -25,6 +35,15 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 __device__ __forceinline__ float slice_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
+}
+
+__device__ __forceinline__ double softplus_f(double x) { return x > 40.0 ? x : log1p(exp(x)); }
+
+__device__ __forceinline__ double slice_sum(double v) {
     v += __shfl_xor_sync(0xffffffffu, v, 1);
     v += __shfl_xor_sync(0xffffffffu, v, 2);
     v += __shfl_xor_sync(0xffffffffu, v, 4);
@@ -88,7 +107,7 @@ __global__ void conv_tail_update_kernel(const float* __restrict__ pre, int ld, i
 // pre[:, dt_offset + head] the raw step sizes. Per head, with B and C of the head's group:
 //   dt = softplus(raw + dt_bias);  S <- exp(neg_rate * dt) S + dt * B x^T;  y = S^T C + skip * x
 // S is [n_state][vdim] at cells[slot][(head * n_state + n) * vdim + p].
-template <int NPT>
+template <int NPT, typename S>
 __global__ void __launch_bounds__(512)
 mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ pre, int pre_ld,
                    int dt_offset, const float* __restrict__ dt_bias,
@@ -103,8 +122,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ pre,
     float* b_s = sm;                          // [SS_TILE][NP]
     float* c_s = b_s + SS_TILE * NP;          // [SS_TILE][NP]
     float* x_s = c_s + SS_TILE * NP;          // [SS_TILE][cols]
-    float* dt_s = x_s + SS_TILE * cols;       // [SS_TILE]
-    float* da_s = dt_s + SS_TILE;             // [SS_TILE]
+    __shared__ S dt_s[SS_TILE], da_s[SS_TILE];
     const int head = blockIdx.x / chunks_per_head, chunk = blockIdx.x - head * chunks_per_head;
     const int seq = blockIdx.y;
     const int begin = q_start[seq], end = q_start[seq + 1];
@@ -116,11 +134,11 @@ mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ pre,
     const int inner = heads * vdim, width = inner + 2 * groups * n_state;
     const int g = head / (heads / groups);
     float* mine = cells + (int64_t)slots[seq] * cell_stride + (int64_t)head * n_state * vdim;
-    float s[NPT];
+    S s[NPT];
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
         const int n = slice + SS_SLICES * i;
-        s[i] = (live && n < n_state) ? mine[(int64_t)n * vdim + p] : 0.f;
+        s[i] = (live && n < n_state) ? (S)mine[(int64_t)n * vdim + p] : (S)0;
     }
     const float rate = neg_rate[head], bias = dt_bias[head], d_skip = skip[head];
     for (int t0 = begin; t0 < end; t0 += SS_TILE) {
@@ -138,31 +156,35 @@ mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ pre,
             x_s[idx] = pp < vdim ? xbc[(int64_t)(t0 + tt) * width + head * vdim + pp] : 0.f;
         }
         if (tid < nt) {
-            const float dt = softplus_f(pre[(int64_t)(t0 + tid) * pre_ld + dt_offset + head] + bias);
-            dt_s[tid] = dt;
-            da_s[tid] = expf(rate * dt);
+            // in double whatever S is: sixteen numbers a tile, and the decay comes out rounded
+            // to nearest instead of leaning one way
+            const double dt = softplus_f((double)pre[(int64_t)(t0 + tid) * pre_ld + dt_offset + head] +
+                                         (double)bias);
+            dt_s[tid] = (S)dt;
+            da_s[tid] = (S)exp((double)rate * dt);
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
-            const float da = da_s[tt], x = x_s[tt * cols + p_local];
-            const float dtx = dt_s[tt] * x;
+            const float x = x_s[tt * cols + p_local];
+            const S da = da_s[tt];
+            const S dtx = dt_s[tt] * (S)x;
             const float* bt = b_s + tt * NP + slice;
             const float* ct = c_s + tt * NP + slice;
-            float acc = 0.f;
+            S acc = (S)0;
 #pragma unroll
             for (int i = 0; i < NPT; ++i) {
-                s[i] = fmaf(da, s[i], dtx * bt[SS_SLICES * i]);
-                acc = fmaf(s[i], ct[SS_SLICES * i], acc);
+                s[i] = fma(da, s[i], dtx * (S)bt[SS_SLICES * i]);
+                acc = fma(s[i], (S)ct[SS_SLICES * i], acc);
             }
             acc = slice_sum(acc);
             if (slice == 0 && live)
-                y[(int64_t)(t0 + tt) * inner + head * vdim + p] = fmaf(d_skip, x, acc);
+                y[(int64_t)(t0 + tt) * inner + head * vdim + p] = (float)fma((S)d_skip, (S)x, acc);
         }
     }
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
         const int n = slice + SS_SLICES * i;
-        if (live && n < n_state) mine[(int64_t)n * vdim + p] = s[i];
+        if (live && n < n_state) mine[(int64_t)n * vdim + p] = (float)s[i];
     }
 }
 
@@ -176,7 +198,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ pre,
 // computed from the matrix as the token found it (A): S^T k = g A^T k and o = g A^T q +
 // u (k . q), so one pass over a column's rows gives both sums. S is [dim][vdim] at
 // cells[slot][(head * dim + d) * vdim + p].
-template <int DPT>
+template <int DPT, typename S>
 __global__ void __launch_bounds__(512)
 delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ pre, int pre_ld,
                        int beta_offset, int decay_offset, const float* __restrict__ dt_bias,
@@ -193,8 +215,8 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
     float* k_s = q_s + SS_TILE * DP;          // [SS_TILE][DP]
     float* v_s = k_s + SS_TILE * DP;          // [SS_TILE][cols]
     float* beta_s = v_s + SS_TILE * cols;     // [SS_TILE]
-    float* g_s = beta_s + SS_TILE;            // [SS_TILE]
-    float* kq_s = g_s + SS_TILE;              // [SS_TILE]
+    float* kq_s = beta_s + SS_TILE;           // [SS_TILE]
+    __shared__ S g_s[SS_TILE];
     const int head = blockIdx.x / chunks_per_head, chunk = blockIdx.x - head * chunks_per_head;
     const int seq = blockIdx.y;
     const int begin = q_start[seq], end = q_start[seq + 1];
@@ -206,11 +228,11 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
     const int qk = key_heads * dim, inner = heads * vdim, width = 2 * qk + inner;
     const int kh = head / (heads / key_heads);
     float* mine = cells + (int64_t)slots[seq] * cell_stride + (int64_t)head * dim * vdim;
-    float s[DPT];
+    S s[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = slice + SS_SLICES * i;
-        s[i] = (live && d < dim) ? mine[(int64_t)d * vdim + p] : 0.f;
+        s[i] = (live && d < dim) ? (S)mine[(int64_t)d * vdim + p] : (S)0;
     }
     const float rate = neg_rate[head], bias = dt_bias[head];
     const float q_scale = 1.f / sqrtf((float)dim);
@@ -231,7 +253,7 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
         if (tid < nt) {
             const float* row = pre + (int64_t)(t0 + tid) * pre_ld;
             beta_s[tid] = 1.f / (1.f + expf(-row[beta_offset + head]));
-            g_s[tid] = expf(rate * softplus_f(row[decay_offset + head] + bias));
+            g_s[tid] = (S)exp((double)rate * softplus_f((double)row[decay_offset + head] + (double)bias));
         }
         __syncthreads();
         // unit vectors, and the token's k . q
@@ -257,26 +279,26 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
         for (int tt = 0; tt < nt; ++tt) {
             const float* qt = q_s + tt * DP + slice;
             const float* kt = k_s + tt * DP + slice;
-            float a = 0.f, b = 0.f;
+            S a = (S)0, b = (S)0;
 #pragma unroll
             for (int i = 0; i < DPT; ++i) {
-                a = fmaf(s[i], kt[SS_SLICES * i], a);
-                b = fmaf(s[i], qt[SS_SLICES * i], b);
+                a = fma(s[i], (S)kt[SS_SLICES * i], a);
+                b = fma(s[i], (S)qt[SS_SLICES * i], b);
             }
             a = slice_sum(a);
             b = slice_sum(b);
-            const float g = g_s[tt];
-            const float u = beta_s[tt] * (v_s[tt * cols + p_local] - g * a);
+            const S g = g_s[tt];
+            const S u = (S)beta_s[tt] * ((S)v_s[tt * cols + p_local] - g * a);
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) s[i] = fmaf(g, s[i], kt[SS_SLICES * i] * u);
+            for (int i = 0; i < DPT; ++i) s[i] = fma(g, s[i], (S)kt[SS_SLICES * i] * u);
             if (slice == 0 && live)
-                out[(int64_t)(t0 + tt) * inner + head * vdim + p] = fmaf(u, kq_s[tt], g * b);
+                out[(int64_t)(t0 + tt) * inner + head * vdim + p] = (float)fma(u, (S)kq_s[tt], g * b);
         }
     }
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = slice + SS_SLICES * i;
-        if (live && d < dim) mine[(int64_t)d * vdim + p] = s[i];
+        if (live && d < dim) mine[(int64_t)d * vdim + p] = (float)s[i];
     }
 }
 
@@ -356,7 +378,7 @@ MB_EXPORT int mb_mamba2_scan(const float* xbc, const float* pre, int pre_ld, int
                              const float* dt_bias, const float* neg_rate, const float* skip,
                              float* cells, long long cell_stride, const int* q_start,
                              const int* slots, float* y, int num_seqs, int heads, int vdim,
-                             int n_state, int groups, void* stream) {
+                             int n_state, int groups, int precise, void* stream) {
     if (num_seqs <= 0) return MB_OK;
     if (heads <= 0 || vdim <= 0 || n_state <= 0 || n_state > 256 || groups <= 0 || heads % groups ||
         num_seqs > 65535)
@@ -367,11 +389,16 @@ MB_EXPORT int mb_mamba2_scan(const float* xbc, const float* pre, int pre_ld, int
     cudaStream_t s = (cudaStream_t)stream;
 #define MB_M2_CASE(NPT)                                                                            \
     do {                                                                                           \
-        const size_t smem = (size_t)(2 * SS_TILE * NPT * SS_SLICES + SS_TILE * warps * 4 +         \
-                                     2 * SS_TILE) * sizeof(float);                                 \
-        MB_LAUNCH((mamba2_scan_kernel<NPT>), grid, warps * 32, smem, s, xbc, pre, pre_ld, dt_offset, \
-                  dt_bias, neg_rate, skip, cells, (int64_t)cell_stride, q_start, slots, y, heads,  \
-                  vdim, n_state, groups, chunks);                                                  \
+        const size_t smem = (size_t)(2 * SS_TILE * NPT * SS_SLICES + SS_TILE * warps * 4) *        \
+                            sizeof(float);                                                         \
+        if (precise)                                                                               \
+            MB_LAUNCH((mamba2_scan_kernel<NPT, double>), grid, warps * 32, smem, s, xbc, pre, pre_ld,  \
+                      dt_offset, dt_bias, neg_rate, skip, cells, (int64_t)cell_stride, q_start,    \
+                      slots, y, heads, vdim, n_state, groups, chunks);                             \
+        else                                                                                       \
+            MB_LAUNCH((mamba2_scan_kernel<NPT, float>), grid, warps * 32, smem, s, xbc, pre, pre_ld,   \
+                      dt_offset, dt_bias, neg_rate, skip, cells, (int64_t)cell_stride, q_start,    \
+                      slots, y, heads, vdim, n_state, groups, chunks);                             \
     } while (0)
     if (n_state <= 16) MB_M2_CASE(2);
     else if (n_state <= 32) MB_M2_CASE(4);
@@ -386,7 +413,8 @@ MB_EXPORT int mb_delta_rule_scan(const float* qkv, const float* pre, int pre_ld,
                                  int decay_offset, const float* dt_bias, const float* neg_rate,
                                  float unit_eps, float* cells, long long cell_stride,
                                  const int* q_start, const int* slots, float* out, int num_seqs,
-                                 int heads, int key_heads, int dim, int vdim, void* stream) {
+                                 int heads, int key_heads, int dim, int vdim, int precise,
+                                 void* stream) {
     if (num_seqs <= 0) return MB_OK;
     if (heads <= 0 || key_heads <= 0 || heads % key_heads || dim <= 0 || dim > 256 || vdim <= 0 ||
         num_seqs > 65535)
@@ -398,10 +426,17 @@ MB_EXPORT int mb_delta_rule_scan(const float* qkv, const float* pre, int pre_ld,
 #define MB_DR_CASE(DPT)                                                                            \
     do {                                                                                           \
         const size_t smem = (size_t)(2 * SS_TILE * DPT * SS_SLICES + SS_TILE * warps * 4 +         \
-                                     3 * SS_TILE) * sizeof(float);                                 \
-        MB_LAUNCH((delta_rule_scan_kernel<DPT>), grid, warps * 32, smem, s, qkv, pre, pre_ld,      \
-                  beta_offset, decay_offset, dt_bias, neg_rate, unit_eps, cells,                   \
-                  (int64_t)cell_stride, q_start, slots, out, heads, key_heads, dim, vdim, chunks); \
+                                     2 * SS_TILE) * sizeof(float);                                 \
+        if (precise)                                                                               \
+            MB_LAUNCH((delta_rule_scan_kernel<DPT, double>), grid, warps * 32, smem, s, qkv, pre,  \
+                      pre_ld, beta_offset, decay_offset, dt_bias, neg_rate, unit_eps, cells,       \
+                      (int64_t)cell_stride, q_start, slots, out, heads, key_heads, dim, vdim,      \
+                      chunks);                                                                     \
+        else                                                                                       \
+            MB_LAUNCH((delta_rule_scan_kernel<DPT, float>), grid, warps * 32, smem, s, qkv, pre,   \
+                      pre_ld, beta_offset, decay_offset, dt_bias, neg_rate, unit_eps, cells,       \
+                      (int64_t)cell_stride, q_start, slots, out, heads, key_heads, dim, vdim,      \
+                      chunks);                                                                     \
     } while (0)
     if (dim <= 16) MB_DR_CASE(2);
     else if (dim <= 32) MB_DR_CASE(4);

@@ -112,10 +112,10 @@ _SIGNATURES = {
                             c_int, c_int, c_void_p],
     "mb_mamba2_scan": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                       c_void_p],
+                       c_int, c_void_p],
     "mb_delta_rule_scan": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
                            c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                           c_int, c_int, c_void_p],
+                           c_int, c_int, c_int, c_void_p],
     "mb_gated_group_norm": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float,
                             c_int, c_void_p, c_int, c_int, c_void_p],
     "mb_latent_norm_store": [c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p,

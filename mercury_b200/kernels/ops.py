@@ -647,29 +647,33 @@ class CudaOps:
         self.launches += 1
 
     @_timed("recurrence")
-    def mamba2_scan(self, xbc, pre, dt_offset, dt_bias, neg_rate, skip, layout, cells, batch, y):
+    def mamba2_scan(self, xbc, pre, dt_offset, dt_bias, neg_rate, skip, layout, cells, batch, y,
+                    precise=False):
         """S <- exp(neg_rate dt) S + dt B x^T, y = S^T C + skip x per head, dt = softplus(pre[:,
         dt_offset + head] + dt_bias); xbc = [x | B | C]; `cells` [slots, heads * state * vdim]
-        is a view of the state rows; everything float32."""
+        is a view of the state rows; everything float32. `precise`: the matrices are held in
+        double while the step runs (the float32 engine; see csrc/state_space.cu)."""
         heads, vdim, n_state, groups = layout
         check(self.lib.mb_mamba2_scan(
             _ptr(xbc), _ptr(pre), pre.shape[1], int(dt_offset), _ptr(dt_bias), _ptr(neg_rate),
             _ptr(skip), _ptr(cells), cells.stride(0), _ptr(batch.q_start), _ptr(batch.slots), _ptr(y),
-            batch.num_seqs, heads, vdim, n_state, groups, self._stream()), "mamba2_scan")
+            batch.num_seqs, heads, vdim, n_state, groups, int(bool(precise)), self._stream()),
+            "mamba2_scan")
         self.launches += 1
 
     @_timed("recurrence")
     def delta_rule_scan(self, qkv, pre, beta_offset, decay_offset, dt_bias, neg_rate, layout,
-                        unit_eps, cells, batch, o):
+                        unit_eps, cells, batch, o, precise=False):
         """The gated delta rule per head over qkv = [q | k | v]; beta and the decay are read
         off pre[:, beta_offset + head] and pre[:, decay_offset + head]; `cells` [slots, heads *
-        dim * vdim] is a view of the state rows; everything float32."""
+        dim * vdim] is a view of the state rows; everything float32 (`precise` as in
+        `mamba2_scan`)."""
         heads, key_heads, dim, vdim = layout
         check(self.lib.mb_delta_rule_scan(
             _ptr(qkv), _ptr(pre), pre.shape[1], int(beta_offset), int(decay_offset), _ptr(dt_bias),
             _ptr(neg_rate), float(unit_eps), _ptr(cells), cells.stride(0), _ptr(batch.q_start),
-            _ptr(batch.slots), _ptr(o), batch.num_seqs, heads, key_heads, dim, vdim, self._stream()),
-            "delta_rule_scan")
+            _ptr(batch.slots), _ptr(o), batch.num_seqs, heads, key_heads, dim, vdim,
+            int(bool(precise)), self._stream()), "delta_rule_scan")
         self.launches += 1
 
     @_timed("recurrence")

@@ -212,7 +212,7 @@ class Mamba2(Mixer):
         y = ctx.buffer("recurrent_y", tokens, self.inner, dtype="float32")
         ops.mamba2_scan(xbc, pre, self.proj - self.heads, self.dt_bias, self.neg_rate, self.skip,
                         (self.heads, self.head_dim, self.state_size, self.groups), cells,
-                        ctx.batch, y)
+                        ctx.batch, y, precise=ctx.dtype == torch.float32)
         mixed = ctx.buffer("recurrent_mixed", tokens, self.inner)
         ops.gated_group_norm(y, pre, 0, self.norm_weight, self.norm_groups, self.eps, True, mixed)
         out = ctx.buffer("sublayer_out", tokens, self.hidden_size, dtype="float32")
@@ -284,7 +284,7 @@ class GatedDeltaRule(Mixer):
         ops.delta_rule_scan(qkv, pre, gate_at + self.inner, gate_at + self.inner + self.heads,
                             self.dt_bias, self.neg_rate,
                             (self.heads, self.key_heads, self.key_dim, self.head_dim),
-                            self.unit_eps, cells, ctx.batch, o)
+                            self.unit_eps, cells, ctx.batch, o, precise=ctx.dtype == torch.float32)
         mixed = ctx.buffer("recurrent_mixed", tokens, self.inner)
         ops.gated_group_norm(o, pre, gate_at, self.norm_weight, self.heads, self.eps, False, mixed)
         out = ctx.buffer("sublayer_out", tokens, self.hidden_size, dtype="float32")

@@ -383,7 +383,8 @@ class TorchOps:
             history = torch.cat([old, x])[-(taps - 1):]
             tail[slot] = history.flip(0).reshape(-1)
 
-    def mamba2_scan(self, xbc, pre, dt_offset, dt_bias, neg_rate, skip, layout, cells, batch, y):
+    def mamba2_scan(self, xbc, pre, dt_offset, dt_bias, neg_rate, skip, layout, cells, batch, y,
+                    precise=False):
         heads, vdim, n, groups = layout
         inner, per = heads * vdim, heads // groups
         for begin, end, slot in self._sequences(batch):
@@ -402,7 +403,7 @@ class TorchOps:
             cells[slot] = s.reshape(-1).to(cells.dtype)
 
     def delta_rule_scan(self, qkv, pre, beta_offset, decay_offset, dt_bias, neg_rate, layout,
-                        unit_eps, cells, batch, o):
+                        unit_eps, cells, batch, o, precise=False):
         heads, key_heads, dim, vdim = layout
         qk, per = key_heads * dim, heads // key_heads
         for begin, end, slot in self._sequences(batch):

@@ -70,7 +70,8 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
                      int max_pages, const int* __restrict__ q_start,
                      const int* __restrict__ kv_len_of, __nv_bfloat16* __restrict__ out,
                      float* __restrict__ part_acc, float* __restrict__ part_ml, int n_q, int n_kv,
-                     int page_size, float scale, int window, int tiles_per_seq, int num_splits) {
+                     int page_size, float scale, int window, int tiles_per_seq, int num_splits,
+                     const float* __restrict__ sinks) {
     grid_dependency_sync();
     constexpr int ROWS = NWARPS * 16;
     constexpr int CH = D / 8;        // 16-byte chunks per row
@@ -290,7 +291,11 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
         const int tok = row / group, hg = row - tok * group;
         const int64_t flat = (int64_t)(q_begin + tok) * n_q + kvh * group + hg;
         if (num_splits == 1) {
-            const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+            // a sink: exp(sink) beside the keys' exp(score) in the denominator (base 2 here)
+            float denom = l[h];
+            if (sinks && m[h] > -INFINITY)
+                denom += fast_exp2(sinks[kvh * group + hg] * 1.4426950408889634f - m[h]);
+            const float inv = denom > 0.f ? 1.f / denom : 0.f;
 #pragma unroll
             for (int i = 0; i < D / 8; ++i) {
                 __nv_bfloat162 v = __floats2bfloat162_rn(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
@@ -675,7 +680,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                                 __nv_bfloat16* __restrict__ out, int n_q, int n_kv, int page_size,
                                 float scale, int window, const float* __restrict__ cos_t,
                                 const float* __restrict__ sin_t, int raw, int store,
-                                int* __restrict__ error) {
+                                int* __restrict__ error, const float* __restrict__ sinks) {
     // raw: q, k and v in `qkv` are the projection as it came out of the product (bias added,
     // not rotated, nothing stored): this kernel rotates the queries as it loads them, and the
     // block whose key range holds this step's positions rotates the new keys, writes them and
@@ -1384,6 +1389,10 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
             wgt[w] = ml_red[w][r][0] > -INFINITY ? fast_exp2(ml_red[w][r][0] - big) : 0.f;
             sum += ml_red[w][r][1] * wgt[w];
         }
+        // a sink joins the denominator once: here when the block has all the keys, else where
+        // the ranges are merged
+        if (sinks && num_splits == 1 && r < rows && big > -INFINITY)
+            sum += fast_exp2(sinks[kvh * group + hg] * 1.4426950408889634f - big);
         if (PUSH && num_splits > 1) {
             // row r is finished by block r / per_block: its landing slot for this range
             const int per_block = (16 + (int)num_splits - 1) / (int)num_splits;
@@ -1470,6 +1479,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                 denom += w * lz[z];
             }
             const int tok = r / group, hg = r - tok * group;
+            if (sinks && big > -INFINITY) denom += fast_exp2(sinks[kvh * group + hg] * 1.4426950408889634f - big);
             out[((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + c] =
                 __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
         }
@@ -1512,6 +1522,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                 denom += w * lz[z];
             }
             const int tok = r / group, hg = r - tok * group;
+            if (sinks && big > -INFINITY) denom += fast_exp2(sinks[kvh * group + hg] * 1.4426950408889634f - big);
             out[((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + c] =
                 __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
         }
@@ -1538,7 +1549,7 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
                                     const int* q_start, const int* kv_len, void* out, int n_q, int n_kv,
                                     int page_size, float scale, int window, int num_seqs, int cluster,
                                     const float* cos_t, const float* sin_t, int raw, int store,
-                                    int num_pages, int* error, cudaStream_t s) {
+                                    int num_pages, int* error, const float* sinks, cudaStream_t s) {
     constexpr int STAGES = FED ? 4 : STG;
     CUtensorMap map_k, map_v;
     memset(&map_k, 0, sizeof(map_k));
@@ -1583,7 +1594,7 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
     cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D, FED, TWO, STG>, map_k, map_v, (const bf*)qkv,
                        q_row_stride, (const bf*)k_pages, (const bf*)v_pages, table, max_pages, q_start,
                        kv_len, (bf*)out, n_q, n_kv, page_size, scale, window, cos_t, sin_t, raw, store,
-                       error);
+                       error, sinks);
     return launch_status();
 }
 
@@ -1616,7 +1627,7 @@ int launch_attention_mma(const void* qkv, int q_row_stride, const void* k_pages,
                          const int* table, int max_pages, const int* q_start, const int* kv_len,
                          void* out, float* part_acc, float* part_ml, int n_q, int n_kv,
                          int page_size, float scale, int window, int num_seqs, int max_q_len,
-                         int num_splits, cudaStream_t s) {
+                         int num_splits, const float* sinks, cudaStream_t s) {
     constexpr int ROWS = NWARPS * 16;
     const size_t smem = (size_t)(ROWS * D + 4 * MMA_BN * D) * sizeof(__nv_bfloat16);
     static bool raised = false;
@@ -1634,7 +1645,7 @@ int launch_attention_mma(const void* qkv, int q_row_stride, const void* k_pages,
     MB_LAUNCH((attention_mma_kernel<D, NWARPS>), grid, NWARPS * 32, smem, s, 
         (const bf*)qkv, q_row_stride, (const bf*)k_pages, (const bf*)v_pages, table, max_pages,
         q_start, kv_len, (bf*)out, part_acc, part_ml, n_q, n_kv, page_size, scale, window,
-        tiles_per_seq, num_splits);
+        tiles_per_seq, num_splits, sinks);
     return launch_status();
 }
 
@@ -1661,14 +1672,13 @@ MB_EXPORT int mb_attention_decode_raw_pays(int d) { return d == 64 || d == 128; 
 // bare projection: the kernel rotates with `cos_t` / `sin_t` ([positions, d/2], null = no
 // rotation, the whole head otherwise) and, with `store`, writes this step's keys and values
 // into the pages itself.
-MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_stride, const void* k_pages,
-                                                const void* v_pages, const int* table, int max_pages,
-                                                const int* q_start, const int* kv_len, void* out,
-                                                int tokens, int num_seqs, int max_q_len, int n_q,
-                                                int n_kv, int d, int page_size, float scale, int window,
-                                                int cluster, const float* cos_t, const float* sin_t,
-                                                int raw, int store, int num_pages, int* error,
-                                                void* stream) {
+// `sinks`: null, or one float32 per query head whose exponential joins the softmax's denominator.
+MB_EXPORT int mb_paged_attention_decode_cluster_sinks(
+    const void* qkv, int q_row_stride, const void* k_pages, const void* v_pages, const int* table,
+    int max_pages, const int* q_start, const int* kv_len, void* out, int tokens, int num_seqs,
+    int max_q_len, int n_q, int n_kv, int d, int page_size, float scale, int window, int cluster,
+    const float* cos_t, const float* sin_t, int raw, int store, int num_pages, int* error,
+    const float* sinks, void* stream) {
     // num_pages > 0 (with the pages' count) and `error` (a zeroed word on the device) select
     // the TMA-fed form (pages of 8 to 64 tokens): for blocks that walk many key tiles each
     // (large batches). 0: the copies are 16 bytes per thread, as the small batches want them,
@@ -1693,7 +1703,7 @@ MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_strid
     launch_attention_decode_cluster<D_, FED_, TWO_, STG_>(qkv, q_row_stride, k_pages, v_pages, table, max_pages, \
                                                     q_start, kv_len, out, n_q, n_kv, page_size, scale, \
                                                     window, num_seqs, cluster, cos_t, sin_t, raw, store, \
-                                                    FED_ ? num_pages : 0, FED_ ? error : nullptr, s)
+                                                    FED_ ? num_pages : 0, FED_ ? error : nullptr, sinks, s)
     // (TMA-fed: eight half stages at head size 64, four at 128, where eight would leave an SM
     // to one block: measured at 1.5B sizes with no more blocks than SMs, 8 sequences, 1.32 ms per
     // step with four and 1.44 with eight)
@@ -1711,14 +1721,30 @@ MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_strid
 #undef MB_DC_LAUNCH
 }
 
-// Same arguments as mb_paged_attention_simt; bfloat16 only. Scratch as there.
-MB_EXPORT int mb_paged_attention_mma(const void* qkv, int q_row_stride, const void* k_pages,
-                                     const void* v_pages, const int* table, int max_pages,
-                                     const int* q_start, const int* kv_len, const int* seq_of_token,
-                                     void* out, float* scratch, long long scratch_floats, int tokens,
-                                     int num_seqs, int max_q_len, int n_q, int n_kv, int d,
-                                     int page_size, float scale, int window, int num_splits,
-                                     int* counters, void* stream) {
+MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_stride, const void* k_pages,
+                                                const void* v_pages, const int* table, int max_pages,
+                                                const int* q_start, const int* kv_len, void* out,
+                                                int tokens, int num_seqs, int max_q_len, int n_q,
+                                                int n_kv, int d, int page_size, float scale, int window,
+                                                int cluster, const float* cos_t, const float* sin_t,
+                                                int raw, int store, int num_pages, int* error,
+                                                void* stream) {
+    return mb_paged_attention_decode_cluster_sinks(qkv, q_row_stride, k_pages, v_pages, table, max_pages,
+                                                   q_start, kv_len, out, tokens, num_seqs, max_q_len, n_q,
+                                                   n_kv, d, page_size, scale, window, cluster, cos_t, sin_t,
+                                                   raw, store, num_pages, error, nullptr, stream);
+}
+
+// Same arguments as mb_paged_attention_simt_sinks; bfloat16 only. Scratch as there. Sinks are
+// taken by the kernel for prompt portions (more than 16 rows per key/value head) only.
+MB_EXPORT int mb_paged_attention_mma_sinks(const void* qkv, int q_row_stride, const void* k_pages,
+                                           const void* v_pages, const int* table, int max_pages,
+                                           const int* q_start, const int* kv_len,
+                                           const int* seq_of_token, void* out, float* scratch,
+                                           long long scratch_floats, int tokens, int num_seqs,
+                                           int max_q_len, int n_q, int n_kv, int d, int page_size,
+                                           float scale, int window, int num_splits, int* counters,
+                                           const float* sinks, void* stream) {
     // counters: num_seqs * n_kv zeroed ints (left zeroed) to let the last split block merge
     // in the same launch; null selects the separate merge kernel.
     if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
@@ -1739,6 +1765,7 @@ MB_EXPORT int mb_paged_attention_mma(const void* qkv, int q_row_stride, const vo
     const int group = n_q / n_kv;
     const bool small = max_q_len * group <= 16;  // decode-like: one warp of rows per block
     int rc;
+    if (small && sinks) return MB_ERR_UNSUPPORTED_SIZE;
     if (small) {
         if (num_splits > 64) counters = nullptr;   // the in-kernel merge holds 64 splits
         if (d == 64)
@@ -1757,7 +1784,7 @@ MB_EXPORT int mb_paged_attention_mma(const void* qkv, int q_row_stride, const vo
 #define MB_MMA_CASE(DD, NW)                                                                       \
     rc = launch_attention_mma<DD, NW>(qkv, q_row_stride, k_pages, v_pages, table, max_pages,      \
                                       q_start, kv_len, out, part_acc, part_ml, n_q, n_kv,         \
-                                      page_size, scale, window, num_seqs, max_q_len, num_splits, s)
+                                      page_size, scale, window, num_seqs, max_q_len, num_splits, sinks, s)
     if (d == 64) {
         MB_MMA_CASE(64, 4);
     } else {
@@ -1766,5 +1793,18 @@ MB_EXPORT int mb_paged_attention_mma(const void* qkv, int q_row_stride, const vo
 #undef MB_MMA_CASE
     if (rc != MB_OK || num_splits == 1) return rc;
     return launch_attention_combine(part_acc, part_ml, seq_of_token, out, tokens, n_q, d, num_splits,
-                                    MB_BF16, s);
+                                    MB_BF16, s, sinks);
+}
+
+MB_EXPORT int mb_paged_attention_mma(const void* qkv, int q_row_stride, const void* k_pages,
+                                     const void* v_pages, const int* table, int max_pages,
+                                     const int* q_start, const int* kv_len, const int* seq_of_token,
+                                     void* out, float* scratch, long long scratch_floats, int tokens,
+                                     int num_seqs, int max_q_len, int n_q, int n_kv, int d,
+                                     int page_size, float scale, int window, int num_splits,
+                                     int* counters, void* stream) {
+    return mb_paged_attention_mma_sinks(qkv, q_row_stride, k_pages, v_pages, table, max_pages, q_start,
+                                        kv_len, seq_of_token, out, scratch, scratch_floats, tokens,
+                                        num_seqs, max_q_len, n_q, n_kv, d, page_size, scale, window,
+                                        num_splits, counters, nullptr, stream);
 }

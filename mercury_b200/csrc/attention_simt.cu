@@ -274,6 +274,9 @@ int dispatch_attention(int nc, const void* qkv, int q_row_stride, const void* k_
         MB_ATT_CASE(6);
         MB_ATT_CASE(7);
         MB_ATT_CASE(8);
+        MB_ATT_CASE(10);
+        MB_ATT_CASE(12);
+        MB_ATT_CASE(16);
     }
 #undef MB_ATT_CASE
     return MB_ERR_UNSUPPORTED_SIZE;
@@ -308,7 +311,7 @@ MB_EXPORT long long mb_attention_scratch_floats(int tokens, int n_q, int d, int 
 
 // max_q_len: the most query tokens one sequence has in this batch (sizes the grid).
 // scratch: float32 buffer of at least mb_attention_scratch_floats() (may be null when
-// num_splits is 1). Head sizes up to 256 are taken; anything else is refused.
+// num_splits is 1). Head sizes up to 512 are taken; anything else is refused.
 // `sinks`: null, or one float32 number per query head whose exponential joins the softmax's
 // denominator (it has no key and no value and is not scaled).
 MB_EXPORT int mb_paged_attention_simt_sinks(const void* qkv, int q_row_stride, const void* k_pages,
@@ -320,7 +323,7 @@ MB_EXPORT int mb_paged_attention_simt_sinks(const void* qkv, int q_row_stride, c
                                             float scale, int window, int num_splits, int dtype,
                                             const float* sinks, void* stream) {
     if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
-    if (d <= 0 || d > 256 || n_kv <= 0 || n_q % n_kv) return MB_ERR_UNSUPPORTED_SIZE;
+    if (d <= 0 || d > 512 || n_kv <= 0 || n_q % n_kv) return MB_ERR_UNSUPPORTED_SIZE;
     if (page_size <= 0 || (page_size & (page_size - 1))) return MB_ERR_UNSUPPORTED_SIZE;
     if (num_splits < 1) num_splits = 1;
     if (n_kv > 65535 || num_splits > 65535) return MB_ERR_UNSUPPORTED_SIZE;
@@ -334,7 +337,8 @@ MB_EXPORT int mb_paged_attention_simt_sinks(const void* qkv, int q_row_stride, c
         part_acc = scratch;
         part_ml = scratch + (int64_t)tokens * n_q * num_splits * d;
     }
-    const int nc = (d + 31) / 32;
+    int nc = (d + 31) / 32;
+    if (nc > 8) nc = nc <= 10 ? 10 : (nc <= 12 ? 12 : 16);      // wide heads (a cached latent)
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
     if (dtype == MB_F32)

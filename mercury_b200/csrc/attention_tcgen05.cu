@@ -86,7 +86,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                      const __grid_constant__ CUtensorMap map_v, const int* __restrict__ table,
                      int max_pages, const int* __restrict__ q_start, const int* __restrict__ kv_len_of,
                      __nv_bfloat16* __restrict__ out, int n_q, int n_kv, int page_size, float scale,
-                     int window, int tiles_per_seq, int* __restrict__ error) {
+                     int window, int tiles_per_seq, int* __restrict__ error,
+                     const float* __restrict__ sinks) {
     constexpr int SUBS = D / 64;                       // 64-feature sub-tiles of a head
     constexpr int S_BUFS = 2;                          // score (and probability) buffers in tensor memory
     constexpr int TB_STAGES = D == 64 ? 4 : 2;         // key/value tiles in flight
@@ -466,6 +467,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         meet();
         l += row_xch[2][half ^ 1][r];
         if (cl_size == 1) {
+            // a sink: exp(sink) beside the keys' exp(score) in the denominator (base 2 here)
+            if (sinks && row_ok && m > -INFINITY)
+                l += tb_exp2(sinks[kvh * group + hg] * 1.4426950408889634f - m);
             const float inv = l > 0.f ? 1.f / l : 0.f;
             __nv_bfloat16* dst = out + ((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + half * (D / 2);
 #pragma unroll 1
@@ -548,6 +552,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 l_all += l_of[k] * weight[k];
             }
             if (row_ok) {
+                if (sinks && m_all > -INFINITY)
+                    l_all += tb_exp2(sinks[kvh * group + hg] * 1.4426950408889634f - m_all);
                 const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
                 __nv_bfloat16* dst = out + ((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D;
 #pragma unroll 1
@@ -624,7 +630,7 @@ static int launch_attention_tcgen05(const void* qkv, int q_row_stride, const voi
                       int num_pages, const int* table, int max_pages, const int* q_start,
                       const int* kv_len, void* out, int tokens, int num_seqs, int max_q_len, int n_q,
                       int n_kv, int page_size, float scale, int window, int cluster, int* error,
-                      cudaStream_t stream) {
+                      const float* sinks, cudaStream_t stream) {
     const int group = n_q / n_kv;
     const int tok_per_tile = TB_ROWS / group;
     CUtensorMap map_q, map_k, map_v;
@@ -673,20 +679,21 @@ static int launch_attention_tcgen05(const void* qkv, int q_row_stride, const voi
     config.numAttrs = num_attrs;
     cudaLaunchKernelEx(&config, attention_tcgen05_kernel<D>, map_q, map_k, map_v, table, max_pages, q_start,
                        kv_len, (__nv_bfloat16*)out, n_q, n_kv, page_size, scale, window, tiles_per_seq,
-                       error);
+                       error, sinks);
     return launch_status();
 }
 
 // qkv: [tokens, q_row_stride] bfloat16 with the rotated queries first; k_pages / v_pages:
 // [num_pages, n_kv, page_size, d]; out: [tokens, n_q * d]. `error` as for mb_gemm_tcgen05
 // (codes 1 producer, 2 and 5 MMA issuer, 3 and 4 softmax). `cluster` (1, 2 or 4) is the
-// number of CTAs that share a row tile and split its keys.
+// number of CTAs that share a row tile and split its keys. `sinks`: null, or one float32 per
+// query head whose exponential joins the softmax's denominator.
 MB_EXPORT int mb_paged_attention_tcgen05(const void* qkv, int q_row_stride, const void* k_pages,
                                      const void* v_pages, int num_pages, const int* table,
                                      int max_pages, const int* q_start, const int* kv_len, void* out,
                                      int tokens, int num_seqs, int max_q_len, int n_q, int n_kv, int d,
                                      int page_size, float scale, int window, int cluster, int* error,
-                                     void* stream) {
+                                     const float* sinks, void* stream) {
     if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
     if (!mb_attention_tcgen05_supports(d, page_size, n_q, n_kv, q_row_stride)) return MB_ERR_UNSUPPORTED_SIZE;
     if (((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) return MB_ERR_ALIGNMENT;
@@ -695,8 +702,8 @@ MB_EXPORT int mb_paged_attention_tcgen05(const void* qkv, int q_row_stride, cons
     if (d == 64)
         return launch_attention_tcgen05<64>(qkv, q_row_stride, k_pages, v_pages, num_pages, table, max_pages, q_start,
                               kv_len, out, tokens, num_seqs, max_q_len, n_q, n_kv, page_size, scale,
-                              window, cluster, error, s);
+                              window, cluster, error, sinks, s);
     return launch_attention_tcgen05<128>(qkv, q_row_stride, k_pages, v_pages, num_pages, table, max_pages, q_start,
                            kv_len, out, tokens, num_seqs, max_q_len, n_q, n_kv, page_size, scale, window,
-                           cluster, error, s);
+                           cluster, error, sinks, s);
 }

@@ -68,7 +68,16 @@ _SIGNATURES = {
                      c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "mb_paged_attention_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                   c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
+                                   c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "mb_paged_attention_decode_cluster_sinks": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                                c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                                c_void_p],
+    "mb_paged_attention_mma_sinks": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
+                                     c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                     c_void_p, c_void_p],
     "mb_paged_attention_decode_cluster": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                           c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,

@@ -957,9 +957,6 @@ class CudaOps:
         group = num_heads // num_kv_heads
         tokens = qkv.shape[0]
         self._check_limits(cache)
-        if sinks is not None:
-            return self._attention_with_sinks(qkv, num_heads, num_kv_heads, head_dim, batch, cache,
-                                              scale, window, out, sinks)
         tc_ok = (qkv.dtype == torch.bfloat16 and self.lib.mb_attention_tcgen05_supports(
             head_dim, cache.page_size, num_heads, num_kv_heads, qkv.shape[1]))
         if kernel == "tcgen05" and not tc_ok:
@@ -974,7 +971,7 @@ class CudaOps:
                 _ptr(out), tokens, batch.num_seqs, batch.max_q_len, num_heads, num_kv_heads,
                 head_dim, cache.page_size, float(scale), int(window),
                 self._prompt_cluster(batch, num_kv_heads, group), _ptr(self._error_word()),
-                self._stream()), "paged_attention (tcgen05)")
+                _ptr(sinks), self._stream()), "paged_attention (tcgen05)")
             self.launches += 1
             self._tc_pending = True
             return
@@ -990,12 +987,19 @@ class CudaOps:
                 if self.decode_clusters and splits < 32 and kernel is None and cache.page_size >= 2:
                     cluster = self._cluster_of(splits)
                     self._decode_cluster(qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale,
-                                         window, out, cluster, None, False)
+                                         window, out, cluster, None, False, sinks)
                     return
+                if sinks is not None:
+                    # so many key ranges that they meet in global memory: the CUDA-core kernel
+                    use_mma = False
+                    splits = self._splits(batch, num_kv_heads, group, 16, 32)
             else:
                 splits = self._prompt_splits(batch, num_kv_heads, group)
         else:
             splits = self._splits(batch, num_kv_heads, group, 16, 32)
+        if sinks is not None and not use_mma:
+            return self._attention_with_sinks(qkv, num_heads, num_kv_heads, head_dim, batch, cache,
+                                              scale, window, out, sinks, splits)
         floats = self.lib.mb_attention_scratch_floats(tokens, num_heads, head_dim, splits)
         scratch = self._scratch_for(floats) if floats else None
         common = (_ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
@@ -1008,8 +1012,8 @@ class CudaOps:
             counters = None
             if splits > 1 and small:
                 counters = self._counters_for(batch.num_seqs * num_kv_heads)
-            check(self.lib.mb_paged_attention_mma(*common, _ptr(counters), self._stream()),
-                  "paged_attention (mma)")
+            check(self.lib.mb_paged_attention_mma_sinks(*common, _ptr(counters), _ptr(sinks),
+                                                        self._stream()), "paged_attention (mma)")
             self.launches += 1 if (splits == 1 or counters is not None) else 2
             return
         else:
@@ -1018,10 +1022,10 @@ class CudaOps:
         self.launches += 1 if splits == 1 else 2
 
     def _attention_with_sinks(self, qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale,
-                              window, out, sinks):
-        group = num_heads // num_kv_heads
+                              window, out, sinks, splits):
+        """The CUDA-core kernel with sinks: the float32 engine, and bfloat16 sizes the
+        tensor-core kernels refuse."""
         tokens = qkv.shape[0]
-        splits = self._splits(batch, num_kv_heads, group, 16, 32)
         floats = self.lib.mb_attention_scratch_floats(tokens, num_heads, head_dim, splits)
         scratch = self._scratch_for(floats) if floats else None
         check(self.lib.mb_paged_attention_simt_sinks(
@@ -1035,20 +1039,20 @@ class CudaOps:
 
     @_timed("attention")
     def _decode_cluster(self, qkv, num_heads, num_kv_heads, head_dim, batch, cache, scale, window,
-                        out, cluster, tables, raw):
+                        out, cluster, tables, raw, sinks=None):
         cos, sin = tables if tables is not None else (None, None)
         self._check_limits(cache, tables)
         # blocks that walk many key tiles each (a large batch) get their tiles by TMA
         fed = self._long_ranges(batch, num_kv_heads, head_dim)
         if fed:
             self._tc_pending = True
-        check(self.lib.mb_paged_attention_decode_cluster(
+        check(self.lib.mb_paged_attention_decode_cluster_sinks(
             _ptr(qkv), qkv.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
             cache.table.shape[1], _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(out),
             qkv.shape[0], batch.num_seqs, batch.max_q_len, num_heads, num_kv_heads, head_dim,
             cache.page_size, float(scale), int(window), cluster, _ptr(cos), _ptr(sin), int(raw),
             int(cache.write), cache.k.shape[0] if fed else 0, _ptr(self._error_word()) if fed else None,
-            self._stream()), "paged_attention (decode clusters)")
+            _ptr(sinks), self._stream()), "paged_attention (decode clusters)")
         self.launches += 1
 
     def _long_ranges(self, batch, num_kv_heads, head_dim=64) -> bool:

@@ -773,14 +773,14 @@ def test_attention_finds_one_far_key(twin, dtype, kernel, splits):
 
 def test_attention_refuses_what_it_cannot_do(ops):
     batch, table = make_batch((1,), (4,), 16, 4)
-    k = torch.zeros((4, 1, 16, 272), dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros((4, 1, 16, 528), dtype=torch.bfloat16, device="cuda")
     cache = LayerCache(k, k.clone(), 16, table, True)
-    qkv = torch.zeros((1, 3 * 272), dtype=torch.bfloat16, device="cuda")
-    out = torch.zeros((1, 272), dtype=torch.bfloat16, device="cuda")
+    qkv = torch.zeros((1, 3 * 528), dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros((1, 528), dtype=torch.bfloat16, device="cuda")
     from mercury_b200.kernels.library import KernelError
 
     with pytest.raises(KernelError):
-        ops.paged_attention(qkv, 1, 1, 272, batch, cache, 1.0, 0, out)
+        ops.paged_attention(qkv, 1, 1, 528, batch, cache, 1.0, 0, out)
 
 
 # ------------------------------------------------------------------------------ sampling

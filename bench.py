@@ -672,6 +672,110 @@ def design_costs(raw: dict, batch: int, context: int, tokens: int) -> dict:
     }
 
 
+KINELIX_SIZES = {
+    # width, heads, head size, latent rank, feed-forward, experts, experts a token uses
+    "0.5b": (896, 14, 64, 128, 4864, 16, 4),
+    "1.5b": (1536, 12, 128, 128, 8960, 16, 4),
+}
+
+
+def kinelix_config(size: str) -> dict:
+    """A Kinelix model at the layer sizes of `size`: attention over a cached latent with a
+    dense feed-forward, a Mamba-2 layer and a gated delta rule with routed experts (whose
+    active width equals the dense feed-forward's), and an attention layer that reads the
+    first one's latent, twice over."""
+    width, heads, dim, rank, ff, experts, top = KINELIX_SIZES[size]
+    moe = {"kind": "moe", "expert": {"ff": ff // top},
+           "router": {"experts": experts, "top": top, "scale": 1.0, "groups": {"count": 4, "keep": 2}}}
+
+    def latent(source=None):
+        mixer = {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": rank, "scale": dim ** -0.5}
+        if source is not None:
+            mixer["kv_from"] = source
+        return mixer
+
+    layers = []
+    for base in range(0, DESIGN_LAYERS, 4):
+        layers += [
+            {"type": "latent_attention", "mixer": latent(), "mlp": {"kind": "dense", "ff": ff}},
+            {"type": "mamba2", "mlp": moe,
+             "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 2,
+                       "norm_groups": 2, "conv": 4}},
+            {"type": "delta", "mlp": moe,
+             "mixer": {"heads": width // 128, "kv_heads": width // 128, "dim": 128, "vdim": 128,
+                       "conv": 4}},
+            {"type": "latent_attention", "mixer": latent(base), "mlp": {"kind": "dense", "ff": ff}},
+        ]
+    return {"architecture": "Kinelix", "width": width, "vocab": DESIGN_VOCAB,
+            "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "max_positions": MODEL_LEN, "layers": layers[:DESIGN_LAYERS]}
+
+
+def kinelix_costs(raw: dict, batch: int, context: int, tokens: int) -> dict:
+    """Per class of kernel call, what a Kinelix model has to read (decode step, bytes) or
+    compute (prompt step, flops; bytes for the classes that only move data)."""
+    w, v = raw["width"], raw["vocab"]
+    products = head = 2 * v * w
+    gated = latent_token = att_flops = head_products = 0
+    expert_all = expert_active = router = state_bytes = scan_flops = rec_tokens = 0
+    norms = 1
+    for layer in raw["layers"]:
+        m = layer["mixer"]
+        norms += 1
+        if layer["type"] == "latent_attention":
+            own = m.get("kv_from") is None
+            rows = m["heads"] * m["dim"] + (m["kv_rank"] if own else 0)
+            products += 2 * (rows * w + m["heads"] * m["vdim"] * w)
+            head_products += 2 * m["heads"] * m["kv_rank"] * (m["dim"] + m["vdim"])
+            latent_token += 2 * m["kv_rank"]
+            att_flops += m["heads"] * 2 * m["kv_rank"]
+        elif layer["type"] == "mamba2":
+            inner = m["heads"] * m["vdim"]
+            proj = 2 * inner + 2 * m["groups"] * m["state"] + m["heads"]
+            products += 2 * (proj * w + inner * w)
+            state_bytes += 2 * 4 * m["heads"] * m["state"] * m["vdim"]
+            scan_flops += 6 * m["heads"] * m["state"] * m["vdim"]
+            rec_tokens += 4 * (2 * proj + 2 * inner) + 2 * inner
+        else:
+            qk, inner = m["kv_heads"] * m["dim"], m["heads"] * m["vdim"]
+            proj = 2 * qk + 2 * inner + 2 * m["heads"]
+            products += 2 * (proj * w + inner * w)
+            state_bytes += 2 * 4 * m["heads"] * m["dim"] * m["vdim"]
+            scan_flops += 8 * m["heads"] * m["dim"] * m["vdim"]
+            rec_tokens += 4 * (2 * proj + 2 * inner) + 2 * inner
+        mlp = layer["mlp"]
+        if mlp is None:
+            continue
+        norms += 1
+        if mlp["kind"] == "dense":
+            gated += 2 * 2 * mlp["ff"] * w
+            products += 2 * mlp["ff"] * w
+        else:
+            r = mlp["router"]
+            expert_all += 2 * 3 * r["experts"] * mlp["expert"]["ff"] * w
+            expert_active += 2 * 3 * r["top"] * mlp["expert"]["ff"] * w
+            router += 4 * r["experts"] * w
+    t = tokens
+    # a decode step reads the experts its tokens chose, at most all of them
+    touched = min(expert_all, batch * expert_active)
+    return {
+        "decode": {"product": ("hbm", products), "gated product": ("hbm", gated),
+                   "attention": ("hbm", batch * context * latent_token),
+                   "head product": ("hbm", head_products),
+                   "expert products": ("hbm", touched), "router": ("hbm", router),
+                   "recurrence": ("hbm", batch * (state_bytes + rec_tokens)),
+                   "norm": ("hbm", norms * batch * w * 14)},
+        "prefill": {"product": ("tensor", t * (products - head) + head),
+                    "gated product": ("tensor", t * gated),
+                    "attention": ("tensor", t * t * att_flops),
+                    "head product": ("tensor", t * head_products),
+                    "expert products": ("tensor", t * expert_active),
+                    "router": ("hbm", router + t * w * 2),
+                    "recurrence": ("tensor", t * scan_flops),
+                    "norm": ("hbm", norms * t * w * 14)},
+    }
+
+
 def classes_of(torch, runner, batch, context, vocab, costs, peak) -> dict:
     """Milliseconds per class of kernel call of a decode step and of a prompt step (events
     around every call, the launches queued behind a delay on the device), with the fraction
@@ -731,7 +835,10 @@ def run_designs(args) -> dict:
     for size in ([args.size] if args.size_given else list(DESIGN_SIZES)):
         row = {}
         fegenex, qwen2 = design_configs(size)
-        for label, raw in (("fegenex", fegenex), ("qwen2", qwen2)):
+        # the design asked for, beside the closest models this engine has at the same sizes
+        models = ((("fegenex", fegenex), ("qwen2", qwen2)) if args.design == "fegenex" else
+                  (("kinelix", kinelix_config(size)), ("fegenex", fegenex), ("qwen2", qwen2)))
+        for label, raw in models:
             _entry, config = config_from_dict(raw)
             tensors = random_tensors(config, SEED, torch.bfloat16)
             vocab = DESIGN_VOCAB
@@ -742,6 +849,7 @@ def run_designs(args) -> dict:
             rate, ms, launches, _ = decode_rate(torch, runner, batch, CONTEXT, vocab, args.steps,
                                                 max(3, args.warmup))
             costs = (design_costs(raw, batch, CONTEXT, PREFILL_TOKENS) if label == "fegenex"
+                     else kinelix_costs(raw, batch, CONTEXT, PREFILL_TOKENS) if label == "kinelix"
                      else class_costs(raw, batch, CONTEXT, PREFILL_TOKENS))
             row[label] = {"prefill_ms": round(prefill_ms, 3),
                           "prefill_tokens_per_s": round(PREFILL_TOKENS / prefill_ms * 1e3, 1),
@@ -890,6 +998,8 @@ def main() -> int:
                    help="run one part only (for profilers and side workloads); prints its own JSON")
     p.add_argument("--size", default=None, choices=tuple(SIZES),
                    help="layer sizes of --only decode/prefill/mixed (default 0.5b; mixed: 1.5b)")
+    p.add_argument("--design", default="fegenex", choices=("fegenex", "kinelix"),
+                   help="which design --only designs measures beside the closest existing models")
     p.add_argument("--policy", default="lpm", choices=("fcfs", "lpm", "lpm_aging"))
     p.add_argument("--batch", type=int, default=BATCH, help="decode batch of --only decode")
     p.add_argument("--no-graphs", action="store_true", help="launch kernels one by one")

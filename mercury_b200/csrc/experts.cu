@@ -40,13 +40,47 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
     }
 }
 
-// A warp per token. Shared memory per warp: s[E], choice[E], group score[E], candidates[E].
-template <typename T>
-__global__ void route_experts_kernel(const T* __restrict__ x, const float* __restrict__ router,
-                                     const float* __restrict__ correction, int* __restrict__ chosen,
-                                     float* __restrict__ weights, int tokens, int hidden,
-                                     int experts, int top, int group_count, int group_keep,
-                                     float route_scale) {
+// Router logits: z[t][e] = Wr[e] . x[t] in float32. A block of eight warps takes RT tokens and
+// eight experts, one expert a warp: a lane reads its share of the expert's row once and
+// multiplies it with the RT tokens' rows (staged in shared memory as float32).
+template <typename T, int RT>
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const T* __restrict__ x, const float* __restrict__ router,
+                     float* __restrict__ logits, int tokens, int hidden, int experts) {
+    grid_dependency_sync();
+    extern __shared__ float x_s[];                 // [RT][hidden]
+    const int t0 = blockIdx.x * RT;
+    for (int idx = threadIdx.x; idx < RT * hidden; idx += blockDim.x) {
+        const int tt = idx / hidden, k = idx - tt * hidden;
+        x_s[idx] = t0 + tt < tokens ? to_float(x[(int64_t)(t0 + tt) * hidden + k]) : 0.f;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int e = blockIdx.y * 8 + warp;
+    if (e >= experts) return;
+    const float* wr = router + (int64_t)e * hidden;
+    float acc[RT];
+#pragma unroll
+    for (int tt = 0; tt < RT; ++tt) acc[tt] = 0.f;
+#pragma unroll 4
+    for (int k = lane; k < hidden; k += 32) {
+        const float wv = __ldg(wr + k);
+#pragma unroll
+        for (int tt = 0; tt < RT; ++tt) acc[tt] = fmaf(x_s[tt * hidden + k], wv, acc[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < RT; ++tt) {
+        const float v = warp_sum(acc[tt]);
+        if (lane == 0 && t0 + tt < tokens) logits[(int64_t)(t0 + tt) * experts + e] = v;
+    }
+}
+
+// The choice, a warp per token. Shared memory per warp: s[E], choice[E], group score[E],
+// candidates[E].
+__global__ void route_select_kernel(const float* __restrict__ logits,
+                                    const float* __restrict__ correction, int* __restrict__ chosen,
+                                    float* __restrict__ weights, int tokens, int experts, int top,
+                                    int group_count, int group_keep, float route_scale) {
     grid_dependency_sync();
     extern __shared__ float sm[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -56,19 +90,12 @@ __global__ void route_experts_kernel(const T* __restrict__ x, const float* __res
     float* choice_s = s_s + experts;
     float* group_s = choice_s + experts;
     float* cand_s = group_s + experts;
-    const T* row = x + (int64_t)t * hidden;
-    for (int e = 0; e < experts; ++e) {
-        const float* wr = router + (int64_t)e * hidden;
-        float acc = 0.f;
-        for (int k = lane; k < hidden; k += 32) acc = fmaf(to_float(row[k]), wr[k], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            const float s = 1.f / (1.f + expf(-acc));
-            s_s[e] = s;
-            choice_s[e] = s + correction[e];
-        }
+    for (int e = lane; e < experts; e += 32) {
+        const float s = 1.f / (1.f + expf(-logits[(int64_t)t * experts + e]));
+        s_s[e] = s;
+        choice_s[e] = s + correction[e];
+        cand_s[e] = -INFINITY;
     }
-    for (int e = lane; e < experts; e += 32) cand_s[e] = -INFINITY;
     __syncwarp();
     const int size = experts / group_count;
     for (int g = lane; g < group_count; g += 32) {
@@ -116,7 +143,7 @@ __global__ void route_experts_kernel(const T* __restrict__ x, const float* __res
 // tile_row0[cap], tile_rows[cap], then perm[pairs] (pair = token * top + choice, grouped by
 // expert; the order inside an expert is arbitrary and changes no result).
 __global__ void __launch_bounds__(1024)
-expert_plan_kernel(const int* __restrict__ chosen, int pairs, int experts, int cap,
+expert_plan_kernel(const int* __restrict__ chosen, int pairs, int experts, int cap, int bm,
                    int* __restrict__ plan) {
     grid_dependency_sync();
     extern __shared__ int ism[];
@@ -137,10 +164,10 @@ expert_plan_kernel(const int* __restrict__ chosen, int pairs, int experts, int c
         int at = 0, tiles = 0;
         for (int e = 0; e < experts; ++e) {
             start_s[e] = at;
-            for (int r = 0; r < count_s[e] && tiles < cap; r += EX_BM) {
+            for (int r = 0; r < count_s[e] && tiles < cap; r += bm) {
                 tile_expert[tiles] = e;
                 tile_row0[tiles] = at + r;
-                tile_rows[tiles] = min(EX_BM, count_s[e] - r);
+                tile_rows[tiles] = min(bm, count_s[e] - r);
                 ++tiles;
             }
             at += count_s[e];
@@ -252,6 +279,184 @@ expert_product_kernel(const TA* __restrict__ a, int a_ld, const TW* __restrict__
     }
 }
 
+
+// ---- the same products on the tensor cores (bfloat16) --------------------------------------
+// mma.sync m16n8k16 with float32 accumulators. A block of four warps takes a tile of TC_BM
+// rows of one expert and TC_BN output columns (in MODE 0 the TC_BN gate rows and the TC_BN up
+// rows of the matrix that belong to them), K in rounds of TC_BK through two shared-memory
+// stages filled by 16-byte cp.async (rows of 128 bytes, the 16-byte pieces of a row permuted
+// by the row's low bits so that ldmatrix meets no bank twice). Rows beyond the tile, columns
+// beyond N and pieces beyond K are filled with zeros by the copy itself. A row's sums do not
+// depend on the other rows of its tile.
+constexpr int TC_BM = 64, TC_BN = 64, TC_BK = 64;
+
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool full) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int bytes = full ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(a));
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+                 "{%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(128)
+expert_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_ld,
+                          const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
+                          const int* __restrict__ plan, int cap, int top, int K, int N) {
+    grid_dependency_sync();
+    const int tile = blockIdx.x;
+    if (tile >= plan[0]) return;
+    const int* tile_expert = plan + 1;
+    const int* tile_row0 = tile_expert + cap;
+    const int* tile_rows = tile_row0 + cap;
+    const int* perm = tile_rows + cap;
+    const int e = tile_expert[tile], row0 = tile_row0[tile], rows = tile_rows[tile];
+    const int n0 = blockIdx.y * TC_BN;
+    constexpr int PARTS = MODE == 0 ? 2 : 1;
+    constexpr int W_ROWS = PARTS * TC_BN;
+    extern __shared__ __align__(128) unsigned char tc_smem[];
+    __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(tc_smem);            // [2][TC_BM][TC_BK]
+    __nv_bfloat16* w_s = a_s + 2 * TC_BM * TC_BK;                               // [2][W_ROWS][TC_BK]
+    __shared__ int src_s[TC_BM];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < TC_BM) {
+        int src = -1;
+        if (tid < rows) src = MODE == 0 ? perm[row0 + tid] / top : row0 + tid;
+        src_s[tid] = src;
+    }
+    __syncthreads();
+    const __nv_bfloat16* we = w + (int64_t)e * (PARTS * N) * K;
+
+    auto fill = [&](int stage, int k0) {
+        // A: TC_BM rows x 8 pieces
+        for (int idx = tid; idx < TC_BM * 8; idx += 128) {
+            const int r = idx >> 3, c = idx & 7;
+            const int src = src_s[r];
+            const bool ok = src >= 0 && k0 + c * 8 < K;
+            const __nv_bfloat16* from = ok ? a + (int64_t)src * a_ld + k0 + c * 8 : a;
+            cp_async_16(a_s + (stage * TC_BM + r) * TC_BK + ((c ^ (r & 7)) * 8), from, ok);
+        }
+        for (int idx = tid; idx < W_ROWS * 8; idx += 128) {
+            const int r = idx >> 3, c = idx & 7;
+            const int part = r / TC_BN, n = n0 + (r - part * TC_BN);
+            const bool ok = n < N && k0 + c * 8 < K;
+            const __nv_bfloat16* from = ok ? we + (int64_t)(part * N + n) * K + k0 + c * 8 : w;
+            cp_async_16(w_s + (stage * W_ROWS + r) * TC_BK + ((c ^ (r & 7)) * 8), from, ok);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    float acc[PARTS][TC_BN / 8][4];
+#pragma unroll
+    for (int p = 0; p < PARTS; ++p)
+#pragma unroll
+        for (int j = 0; j < TC_BN / 8; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[p][j][c] = 0.f;
+
+    const int rounds = (K + TC_BK - 1) / TC_BK;
+    fill(0, 0);
+    for (int kt = 0; kt < rounds; ++kt) {
+        if (kt + 1 < rounds) {
+            fill((kt + 1) & 1, (kt + 1) * TC_BK);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const __nv_bfloat16* as = a_s + ((kt & 1) * TC_BM + warp * 16) * TC_BK;
+        const __nv_bfloat16* ws = w_s + (kt & 1) * W_ROWS * TC_BK;
+#pragma unroll
+        for (int kk = 0; kk < TC_BK / 16; ++kk) {
+            uint32_t af[4];
+            {
+                const int r = lane & 15, c = kk * 2 + (lane >> 4);
+                ldmatrix_x4(af, as + r * TC_BK + ((c ^ (r & 7)) * 8));
+            }
+#pragma unroll
+            for (int p = 0; p < PARTS; ++p) {
+#pragma unroll
+                for (int j2 = 0; j2 < TC_BN / 16; ++j2) {
+                    // two column tiles of 8 at once: lanes 0-15 the first (its two k halves),
+                    // lanes 16-31 the second
+                    uint32_t bf[4];
+                    const int r = p * TC_BN + j2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+                    const int c = kk * 2 + ((lane >> 3) & 1);
+                    ldmatrix_x4(bf, ws + r * TC_BK + ((c ^ (r & 7)) * 8));
+                    mma_bf16_16816(acc[p][2 * j2], af, bf[0], bf[1]);
+                    mma_bf16_16816(acc[p][2 * j2 + 1], af, bf[2], bf[3]);
+                }
+            }
+        }
+        __syncthreads();       // the stage is free before the round after next refills it
+    }
+
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int lr = warp * 16 + g + h * 8;
+        if (lr >= rows) continue;
+        const int64_t dst_row = MODE == 0 ? (int64_t)(row0 + lr) : (int64_t)perm[row0 + lr];
+#pragma unroll
+        for (int j = 0; j < TC_BN / 8; ++j) {
+            const int n = n0 + j * 8 + 2 * t4;
+            if (n >= N) continue;
+            const float v0 = acc[0][j][2 * h], v1 = acc[0][j][2 * h + 1];
+            if (MODE == 0) {
+                const float u0 = acc[PARTS - 1][j][2 * h], u1 = acc[PARTS - 1][j][2 * h + 1];
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + dst_row * N + n;
+                const float r0 = v0 / (1.f + expf(-v0)) * u0, r1 = v1 / (1.f + expf(-v1)) * u1;
+                if (n + 1 < N && (N & 1) == 0)
+                    *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(r0, r1);
+                else {
+                    o[0] = __float2bfloat16_rn(r0);
+                    if (n + 1 < N) o[1] = __float2bfloat16_rn(r1);
+                }
+            } else {
+                float* o = reinterpret_cast<float*>(out) + dst_row * N + n;
+                if (n + 1 < N && (N & 1) == 0)
+                    *reinterpret_cast<float2*>(o) = make_float2(v0, v1);
+                else {
+                    o[0] = v0;
+                    if (n + 1 < N) o[1] = v1;
+                }
+            }
+        }
+    }
+}
+
+template <int MODE>
+int launch_expert_product_mma(const void* a, int a_ld, const void* w, void* out, const int* plan,
+                              int cap, int top, int K, int N, cudaStream_t s) {
+    constexpr int PARTS = MODE == 0 ? 2 : 1;
+    const size_t smem = (size_t)2 * (TC_BM + PARTS * TC_BN) * TC_BK * sizeof(__nv_bfloat16);
+    // (with the kernel's static shared memory this is beyond the 48 KB a launch gets unasked)
+    static bool raised = false;
+    if (!raised) {
+        if (cudaFuncSetAttribute(expert_product_mma_kernel<MODE>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return MB_ERR_UNSUPPORTED_SIZE;
+        raised = true;
+    }
+    dim3 grid(cap, (N + TC_BN - 1) / TC_BN);
+    if (grid.y > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    MB_LAUNCH((expert_product_mma_kernel<MODE>), grid, 128, smem, s, (const __nv_bfloat16*)a, a_ld,
+              (const __nv_bfloat16*)w, out, plan, cap, top, K, N);
+    return launch_status();
+}
+
 // out[t][n] = sum_j weights[t][j] * y[t * top + j][n], j ascending.
 __global__ void expert_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
                                       float* __restrict__ out, int tokens, int top, int hidden) {
@@ -286,11 +491,12 @@ int launch_expert_product(int mode, const void* a, int a_ld, const void* w, void
 
 using namespace mb;
 
-// x_dtype: the activations' type; router and correction are float32.
+// x_dtype: the activations' type; router and correction are float32. `logits`: float32
+// scratch of tokens * experts.
 MB_EXPORT int mb_route_experts(const void* x, int x_dtype, const float* router,
-                               const float* correction, int* chosen, float* weights, int tokens,
-                               int hidden, int experts, int top, int group_count, int group_keep,
-                               float route_scale, void* stream) {
+                               const float* correction, float* logits, int* chosen, float* weights,
+                               int tokens, int hidden, int experts, int top, int group_count,
+                               int group_keep, float route_scale, void* stream) {
     if (tokens <= 0) return MB_OK;
     if (experts <= 0 || top <= 0 || top > experts || group_count <= 0 || experts % group_count ||
         group_keep <= 0 || group_keep > group_count)
@@ -299,45 +505,69 @@ MB_EXPORT int mb_route_experts(const void* x, int x_dtype, const float* router,
     while (warps > 1 && (size_t)warps * 4 * experts * sizeof(float) > 40 * 1024) warps >>= 1;
     const size_t smem = (size_t)warps * 4 * experts * sizeof(float);
     if (smem > 40 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
-    const int blocks = (tokens + warps - 1) / warps;
     cudaStream_t s = (cudaStream_t)stream;
-    if (x_dtype == MB_F32)
-        MB_LAUNCH((route_experts_kernel<float>), blocks, warps * 32, smem, s, (const float*)x, router,
-                  correction, chosen, weights, tokens, hidden, experts, top, group_count, group_keep,
-                  route_scale);
-    else if (x_dtype == MB_BF16)
-        MB_LAUNCH((route_experts_kernel<__nv_bfloat16>), blocks, warps * 32, smem, s,
-                  (const __nv_bfloat16*)x, router, correction, chosen, weights, tokens, hidden, experts,
-                  top, group_count, group_keep, route_scale);
-    else
+    // many tokens: four a block, so that an expert's row is read once for four of them
+    const bool many = tokens > 64 && (size_t)4 * hidden * sizeof(float) <= 48 * 1024;
+    const int rt = many ? 4 : 1;
+    const size_t x_smem = (size_t)rt * hidden * sizeof(float);
+    if (x_smem > 48 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
+    dim3 grid((tokens + rt - 1) / rt, (experts + 7) / 8);
+    if (grid.y > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    typedef __nv_bfloat16 bf;
+    if (x_dtype == MB_F32) {
+        if (many) MB_LAUNCH((router_logits_kernel<float, 4>), grid, 256, x_smem, s, (const float*)x, router, logits, tokens, hidden, experts);
+        else MB_LAUNCH((router_logits_kernel<float, 1>), grid, 256, x_smem, s, (const float*)x, router, logits, tokens, hidden, experts);
+    } else if (x_dtype == MB_BF16) {
+        if (many) MB_LAUNCH((router_logits_kernel<bf, 4>), grid, 256, x_smem, s, (const bf*)x, router, logits, tokens, hidden, experts);
+        else MB_LAUNCH((router_logits_kernel<bf, 1>), grid, 256, x_smem, s, (const bf*)x, router, logits, tokens, hidden, experts);
+    } else {
         return MB_ERR_BAD_DTYPE;
+    }
+    if (cudaGetLastError() != cudaSuccess) return MB_ERR_LAUNCH;
+    MB_LAUNCH((route_select_kernel), (tokens + warps - 1) / warps, warps * 32, smem, s, logits, correction,
+              chosen, weights, tokens, experts, top, group_count, group_keep, route_scale);
     return launch_status();
 }
 
-// The most tiles a step of `pairs` pairs over `experts` experts can have.
-MB_EXPORT int mb_expert_tile_cap(int pairs, int experts) {
-    const int bound = pairs / EX_BM + experts;
+// Rows per tile of the grouped products for this dtype and these sizes: the tensor-core
+// kernel (bfloat16, K a multiple of 8 in both products) takes tiles of 64, the CUDA-core
+// kernel tiles of 32.
+MB_EXPORT int mb_expert_tile_rows(int dtype, int hidden, int ff) {
+    return (dtype == MB_BF16 && hidden % 8 == 0 && ff % 8 == 0) ? TC_BM : EX_BM;
+}
+
+// The most tiles of `bm` rows a step of `pairs` pairs over `experts` experts can have.
+MB_EXPORT int mb_expert_tile_cap(int pairs, int experts, int bm) {
+    const int bound = pairs / bm + experts;
     return pairs < bound ? pairs : bound;
 }
 
 // Integers the plan needs: 1 + 3 * cap + pairs.
-MB_EXPORT int mb_expert_plan(const int* chosen, int pairs, int experts, int cap, int* plan,
+MB_EXPORT int mb_expert_plan(const int* chosen, int pairs, int experts, int cap, int bm, int* plan,
                              void* stream) {
     if (pairs <= 0) return MB_OK;
-    if (experts <= 0 || experts > 4096 || cap <= 0) return MB_ERR_UNSUPPORTED_SIZE;
+    if (experts <= 0 || experts > 4096 || cap <= 0 || bm <= 0) return MB_ERR_UNSUPPORTED_SIZE;
     MB_LAUNCH((expert_plan_kernel), 1, 1024, (size_t)2 * experts * sizeof(int), (cudaStream_t)stream,
-              chosen, pairs, experts, cap, plan);
+              chosen, pairs, experts, cap, bm, plan);
     return launch_status();
 }
 
 // mode 0: gate/up with the SiLU gate (a = the tokens' rows, out = act in the activations'
 // type); mode 1: down (a = act, out = float32 rows per pair). dtype: of a and w alike.
+// `bm`: the tile height the plan was made with (mb_expert_tile_rows), which names the kernel.
 MB_EXPORT int mb_expert_product(int mode, const void* a, int a_ld, const void* w, void* out,
-                                const int* plan, int cap, int top, int K, int N, int dtype,
+                                const int* plan, int cap, int top, int K, int N, int dtype, int bm,
                                 void* stream) {
     if (cap <= 0) return MB_OK;
     if (K <= 0 || N <= 0 || (mode != 0 && mode != 1)) return MB_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    if (bm == TC_BM) {
+        if (dtype != MB_BF16 || K % 8 || a_ld % 8 || (((uintptr_t)a | (uintptr_t)w) & 15))
+            return MB_ERR_ALIGNMENT;
+        return mode == 0 ? launch_expert_product_mma<0>(a, a_ld, w, out, plan, cap, top, K, N, s)
+                         : launch_expert_product_mma<1>(a, a_ld, w, out, plan, cap, top, K, N, s);
+    }
+    if (bm != EX_BM) return MB_ERR_UNSUPPORTED_SIZE;
     if (dtype == MB_F32)
         return launch_expert_product<float, float>(mode, a, a_ld, w, out, plan, cap, top, K, N, s);
     if (dtype == MB_BF16)

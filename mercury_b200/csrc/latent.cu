@@ -64,7 +64,7 @@ head_linear_kernel(const TX* __restrict__ x, int ld, int offset, const TW* __res
     float acc[HL_TOKENS];
 #pragma unroll
     for (int tt = 0; tt < HL_TOKENS; ++tt) acc[tt] = 0.f;
-#pragma unroll 4
+#pragma unroll 16
     for (int i = 0; i < in; ++i) {
         const float v = to_float(wh[(int64_t)i * outs]);
         const float4* row = reinterpret_cast<const float4*>(x_s + i * HL_TOKENS);

@@ -9,11 +9,13 @@
 //
 // Work split of the two scans: a block takes one head of one sequence (and a range of the
 // head's columns p); inside a warp four columns are held by eight lanes each, lane `slice`
-// keeping the matrix rows slice, slice + 8, slice + 16, ... of its column in registers. A
-// token's read-out is a sum over rows: partial sums per lane, then three shuffles. The
-// tokens' inputs are staged through shared memory sixteen tokens at a time, so the block
-// meets once per sixteen tokens. A column's arithmetic is the same however the tokens were
-// cut into steps.
+// keeping the matrix rows 4 (slice + 8 j) + {0, 1, 2, 3}, j = 0, 1, ..., of its column in
+// registers: four neighbouring rows at a time, so that what a token brings for them comes
+// out of shared memory as one 16-byte load (a warp's 32-bit loads of eight distinct words
+// would use a quarter of the memory's width). A token's read-out is a sum over rows: four
+// partial sums per lane, then three shuffles. The tokens' inputs are staged through shared
+// memory thirty-two tokens at a time, so the block meets once per thirty-two tokens. A
+// column's arithmetic is the same however the tokens were cut into steps.
 //
 // The template parameter S is the type the matrix is held in while a step runs. A float32
 // matrix that takes in a thousand tokens one by one gathers a rounding error of some 1e-6 of
@@ -28,11 +30,26 @@
 
 namespace mb {
 
-constexpr int SS_TILE = 16;      // tokens staged at a time
+constexpr int SS_TILE = 32;      // tokens staged at a time
 constexpr int SS_SLICES = 8;     // lanes that share a column
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// One float from global to shared memory without passing through registers (zeros when
+// `take` is false), and the waits that go with it: the scans fetch the next tile of tokens
+// while they walk the one before.
+__device__ __forceinline__ void stage_float(float* dst, const float* src, bool take) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int bytes = take ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void stage_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void stage_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void stage_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+// the matrix row that register i of lane `slice` holds
+__device__ __forceinline__ int row_of(int slice, int i) { return 4 * (slice + SS_SLICES * (i >> 2)) + (i & 3); }
 
 __device__ __forceinline__ float slice_sum(float v) {
     v += __shfl_xor_sync(0xffffffffu, v, 1);
@@ -107,25 +124,39 @@ __global__ void conv_tail_update_kernel(const float* __restrict__ pre, int ld, i
 // pre[:, dt_offset + head] the raw step sizes. Per head, with B and C of the head's group:
 //   dt = softplus(raw + dt_bias);  S <- exp(neg_rate * dt) S + dt * B x^T;  y = S^T C + skip * x
 // S is [n_state][vdim] at cells[slot][(head * n_state + n) * vdim + p].
-template <int NPT, typename S>
+//
+// RUNS = false: a block walks all the step's tokens of its sequence from the state in `cells`.
+// RUNS = true (long portions): the step's tokens of a sequence are cut into runs of `run_len`
+// and block z walks run z from an EMPTY matrix: y gets the run's own part of the read-outs,
+// `run_end` [sequence][run][head][n][p] the matrix the run ends with, `run_decay`
+// [sequence][run][head] the product of its decays and `cum` [token][head] the product of the
+// decays from the run's first token up to each token. Because the decay is one number per
+// head, S_t = cum_t * S(run start) + (what the run itself added): mamba2_carry_kernel chains
+// the runs' starts and mamba2_apply_kernel adds cum_t * C_t^T S(run start) to every y_t.
+template <int NPT, typename S, bool RUNS>
 __global__ void __launch_bounds__(512)
 mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ pre, int pre_ld,
                    int dt_offset, const float* __restrict__ dt_bias,
                    const float* __restrict__ neg_rate, const float* __restrict__ skip,
                    float* __restrict__ cells, int64_t cell_stride, const int* __restrict__ q_start,
                    const int* __restrict__ slots, float* __restrict__ y, int heads, int vdim,
-                   int n_state, int groups, int chunks_per_head) {
+                   int n_state, int groups, int chunks_per_head, int run_len,
+                   float* __restrict__ run_end, float* __restrict__ run_decay,
+                   float* __restrict__ cum) {
     grid_dependency_sync();
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     constexpr int NP = NPT * SS_SLICES;
     const int cols = (blockDim.x >> 5) * 4;
-    float* b_s = sm;                          // [SS_TILE][NP]
-    float* c_s = b_s + SS_TILE * NP;          // [SS_TILE][NP]
-    float* x_s = c_s + SS_TILE * NP;          // [SS_TILE][cols]
+    // two stages of: B [SS_TILE][NP], C [SS_TILE][NP], x [SS_TILE][cols], raw step sizes [SS_TILE]
+    const int stage_floats = 2 * SS_TILE * NP + SS_TILE * cols + SS_TILE;
     __shared__ S dt_s[SS_TILE], da_s[SS_TILE];
     const int head = blockIdx.x / chunks_per_head, chunk = blockIdx.x - head * chunks_per_head;
     const int seq = blockIdx.y;
-    const int begin = q_start[seq], end = q_start[seq + 1];
+    int begin = q_start[seq], end = q_start[seq + 1];
+    if (RUNS) {
+        begin += blockIdx.z * run_len;
+        end = min(end, begin + run_len);
+    }
     if (begin >= end) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int slice = lane & 7, p_local = warp * 4 + (lane >> 3);
@@ -133,58 +164,206 @@ mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ pre,
     const bool live = p < vdim;
     const int inner = heads * vdim, width = inner + 2 * groups * n_state;
     const int g = head / (heads / groups);
-    float* mine = cells + (int64_t)slots[seq] * cell_stride + (int64_t)head * n_state * vdim;
+    float* mine = RUNS ? run_end + (((int64_t)seq * gridDim.z + blockIdx.z) * heads + head) * n_state * vdim
+                       : cells + (int64_t)slots[seq] * cell_stride + (int64_t)head * n_state * vdim;
     S s[NPT];
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
-        const int n = slice + SS_SLICES * i;
-        s[i] = (live && n < n_state) ? (S)mine[(int64_t)n * vdim + p] : (S)0;
+        const int n = row_of(slice, i);
+        s[i] = (!RUNS && live && n < n_state) ? (S)mine[(int64_t)n * vdim + p] : (S)0;
     }
     const float rate = neg_rate[head], bias = dt_bias[head], d_skip = skip[head];
-    for (int t0 = begin; t0 < end; t0 += SS_TILE) {
+    __shared__ float run_cum;                 // product of the run's decays so far
+    if (RUNS && tid == 0) run_cum = 1.f;
+    auto fetch = [&](int stage, int t0) {
+        float* b_to = sm + stage * stage_floats;
+        float* c_to = b_to + SS_TILE * NP;
+        float* x_to = c_to + SS_TILE * NP;
+        float* raw_to = x_to + SS_TILE * cols;
         const int nt = min(SS_TILE, end - t0);
-        __syncthreads();                      // the tile before is consumed
         for (int idx = tid; idx < nt * NP; idx += blockDim.x) {
             const int tt = idx / NP, n = idx - tt * NP;
             const float* row = xbc + (int64_t)(t0 + tt) * width + inner + g * n_state;
-            b_s[idx] = n < n_state ? row[n] : 0.f;
-            c_s[idx] = n < n_state ? row[groups * n_state + n] : 0.f;
+            const bool take = n < n_state;
+            stage_float(b_to + idx, take ? row + n : xbc, take);
+            stage_float(c_to + idx, take ? row + groups * n_state + n : xbc, take);
         }
         for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
             const int tt = idx / cols, pl = idx - tt * cols;
             const int pp = chunk * cols + pl;
-            x_s[idx] = pp < vdim ? xbc[(int64_t)(t0 + tt) * width + head * vdim + pp] : 0.f;
+            const bool take = pp < vdim;
+            stage_float(x_to + idx, take ? xbc + (int64_t)(t0 + tt) * width + head * vdim + pp : xbc, take);
         }
+        if (tid < nt) stage_float(raw_to + tid, pre + (int64_t)(t0 + tid) * pre_ld + dt_offset + head, true);
+        stage_commit();
+    };
+    fetch(0, begin);
+    int turn = 0;
+    for (int t0 = begin; t0 < end; t0 += SS_TILE, turn ^= 1) {
+        const int nt = min(SS_TILE, end - t0);
+        const float* b_s = sm + turn * stage_floats;
+        const float* c_s = b_s + SS_TILE * NP;
+        const float* x_s = c_s + SS_TILE * NP;
+        const float* raw_s = x_s + SS_TILE * cols;
+        // the tile after this one is on its way while this one is walked (its stage was
+        // left by everyone at the end of the turn before)
+        if (t0 + SS_TILE < end) {
+            fetch(turn ^ 1, t0 + SS_TILE);
+            stage_wait_but_one();
+        } else {
+            stage_wait_all();
+        }
+        __syncthreads();
         if (tid < nt) {
-            // in double whatever S is: sixteen numbers a tile, and the decay comes out rounded
+            // in double whatever S is: a few numbers a tile, and the decay comes out rounded
             // to nearest instead of leaning one way
-            const double dt = softplus_f((double)pre[(int64_t)(t0 + tid) * pre_ld + dt_offset + head] +
-                                         (double)bias);
+            const double dt = softplus_f((double)raw_s[tid] + (double)bias);
             dt_s[tid] = (S)dt;
             da_s[tid] = (S)exp((double)rate * dt);
         }
         __syncthreads();
+        if (RUNS && tid == 0 && chunk == 0) {
+            float c = run_cum;
+            for (int tt = 0; tt < nt; ++tt) {
+                c *= (float)da_s[tt];
+                cum[(int64_t)(t0 + tt) * heads + head] = c;
+            }
+            run_cum = c;
+        }
         for (int tt = 0; tt < nt; ++tt) {
             const float x = x_s[tt * cols + p_local];
             const S da = da_s[tt];
             const S dtx = dt_s[tt] * (S)x;
-            const float* bt = b_s + tt * NP + slice;
-            const float* ct = c_s + tt * NP + slice;
-            S acc = (S)0;
+            const float4* bt = reinterpret_cast<const float4*>(b_s + tt * NP) + slice;
+            const float4* ct = reinterpret_cast<const float4*>(c_s + tt * NP) + slice;
+            S part[4] = {(S)0, (S)0, (S)0, (S)0};
 #pragma unroll
-            for (int i = 0; i < NPT; ++i) {
-                s[i] = fma(da, s[i], dtx * (S)bt[SS_SLICES * i]);
-                acc = fma(s[i], (S)ct[SS_SLICES * i], acc);
+            for (int j = 0; j < NPT / 4; ++j) {
+                const float4 bv = bt[SS_SLICES * j], cv = ct[SS_SLICES * j];
+                s[4 * j] = fma(da, s[4 * j], dtx * (S)bv.x);
+                s[4 * j + 1] = fma(da, s[4 * j + 1], dtx * (S)bv.y);
+                s[4 * j + 2] = fma(da, s[4 * j + 2], dtx * (S)bv.z);
+                s[4 * j + 3] = fma(da, s[4 * j + 3], dtx * (S)bv.w);
+                part[0] = fma(s[4 * j], (S)cv.x, part[0]);
+                part[1] = fma(s[4 * j + 1], (S)cv.y, part[1]);
+                part[2] = fma(s[4 * j + 2], (S)cv.z, part[2]);
+                part[3] = fma(s[4 * j + 3], (S)cv.w, part[3]);
             }
-            acc = slice_sum(acc);
+            S acc = slice_sum((part[0] + part[1]) + (part[2] + part[3]));
             if (slice == 0 && live)
                 y[(int64_t)(t0 + tt) * inner + head * vdim + p] = (float)fma((S)d_skip, (S)x, acc);
         }
+        __syncthreads();                      // the stage may be refilled
     }
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
-        const int n = slice + SS_SLICES * i;
+        const int n = row_of(slice, i);
         if (live && n < n_state) mine[(int64_t)n * vdim + p] = (float)s[i];
+    }
+    if (RUNS && tid == 0 && chunk == 0)
+        run_decay[((int64_t)seq * gridDim.z + blockIdx.z) * heads + head] = run_cum;
+}
+
+// The runs' starts, one thread per element of a sequence's matrices: start(0) is the state
+// the step found, start(r + 1) = decay(r) * start(r) + end(r); `run_end` is overwritten with
+// the starts and the state becomes what follows the last run.
+__global__ void mamba2_carry_kernel(float* __restrict__ run_end, const float* __restrict__ run_decay,
+                                    float* __restrict__ cells, int64_t cell_stride,
+                                    const int* __restrict__ q_start, const int* __restrict__ slots,
+                                    int heads, int per_head, int run_len, int max_runs) {
+    grid_dependency_sync();
+    const int seq = blockIdx.y;
+    const int n = q_start[seq + 1] - q_start[seq];
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n <= 0 || e >= heads * per_head) return;
+    const int head = e / per_head;
+    const int runs = (n + run_len - 1) / run_len;
+    float* cell = cells + (int64_t)slots[seq] * cell_stride + e;
+    float carry = *cell;
+    for (int r = 0; r < runs; ++r) {
+        float* at = run_end + ((int64_t)seq * max_runs + r) * heads * per_head + e;
+        const float ended = *at;
+        *at = carry;
+        carry = fmaf(run_decay[((int64_t)seq * max_runs + r) * heads + head], carry, ended);
+    }
+    *cell = carry;
+}
+
+// y_t += cum_t * C_t^T S(run start) for every token of every run: the same split of a head
+// over lanes as the scan, the start held in registers, the tokens' C staged through shared
+// memory.
+template <int NPT>
+__global__ void __launch_bounds__(512)
+mamba2_apply_kernel(const float* __restrict__ xbc, const float* __restrict__ run_start,
+                    const float* __restrict__ cum, const int* __restrict__ q_start,
+                    float* __restrict__ y, int heads, int vdim, int n_state, int groups,
+                    int chunks_per_head, int run_len) {
+    grid_dependency_sync();
+    extern __shared__ __align__(16) float sm[];
+    constexpr int NP = NPT * SS_SLICES;
+    const int cols = (blockDim.x >> 5) * 4;
+    const int stage_floats = SS_TILE * NP + SS_TILE;   // two stages of C [SS_TILE][NP], cum [SS_TILE]
+    const int head = blockIdx.x / chunks_per_head, chunk = blockIdx.x - head * chunks_per_head;
+    const int seq = blockIdx.y;
+    const int begin = q_start[seq] + blockIdx.z * run_len;
+    const int end = min(q_start[seq + 1], begin + run_len);
+    if (begin >= end) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int slice = lane & 7, p = chunk * cols + warp * 4 + (lane >> 3);
+    const bool live = p < vdim;
+    const int inner = heads * vdim, width = inner + 2 * groups * n_state;
+    const int g = head / (heads / groups);
+    const float* mine = run_start + (((int64_t)seq * gridDim.z + blockIdx.z) * heads + head) * n_state * vdim;
+    float s[NPT];
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int n = row_of(slice, i);
+        s[i] = (live && n < n_state) ? mine[(int64_t)n * vdim + p] : 0.f;
+    }
+    auto fetch = [&](int stage, int t0) {
+        float* c_to = sm + stage * stage_floats;
+        float* cum_to = c_to + SS_TILE * NP;
+        const int nt = min(SS_TILE, end - t0);
+        for (int idx = tid; idx < nt * NP; idx += blockDim.x) {
+            const int tt = idx / NP, n = idx - tt * NP;
+            const bool take = n < n_state;
+            stage_float(c_to + idx,
+                        take ? xbc + (int64_t)(t0 + tt) * width + inner + (groups + g) * n_state + n : xbc, take);
+        }
+        if (tid < nt) stage_float(cum_to + tid, cum + (int64_t)(t0 + tid) * heads + head, true);
+        stage_commit();
+    };
+    fetch(0, begin);
+    int turn = 0;
+    for (int t0 = begin; t0 < end; t0 += SS_TILE, turn ^= 1) {
+        const int nt = min(SS_TILE, end - t0);
+        const float* c_s = sm + turn * stage_floats;
+        const float* cum_s = c_s + SS_TILE * NP;
+        if (t0 + SS_TILE < end) {
+            fetch(turn ^ 1, t0 + SS_TILE);
+            stage_wait_but_one();
+        } else {
+            stage_wait_all();
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float4* ct = reinterpret_cast<const float4*>(c_s + tt * NP) + slice;
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < NPT / 4; ++j) {
+                const float4 cv = ct[SS_SLICES * j];
+                part[0] = fmaf(s[4 * j], cv.x, part[0]);
+                part[1] = fmaf(s[4 * j + 1], cv.y, part[1]);
+                part[2] = fmaf(s[4 * j + 2], cv.z, part[2]);
+                part[3] = fmaf(s[4 * j + 3], cv.w, part[3]);
+            }
+            const float acc = slice_sum((part[0] + part[1]) + (part[2] + part[3]));
+            if (slice == 0 && live) {
+                float* at = y + (int64_t)(t0 + tt) * inner + head * vdim + p;
+                *at = fmaf(cum_s[tt], acc, *at);
+            }
+        }
+        __syncthreads();                      // the stage may be refilled
     }
 }
 
@@ -208,14 +387,13 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
                        float* __restrict__ out, int heads, int key_heads, int dim, int vdim,
                        int chunks_per_head) {
     grid_dependency_sync();
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     constexpr int DP = DPT * SS_SLICES;
     const int cols = (blockDim.x >> 5) * 4;
-    float* q_s = sm;                          // [SS_TILE][DP]
-    float* k_s = q_s + SS_TILE * DP;          // [SS_TILE][DP]
-    float* v_s = k_s + SS_TILE * DP;          // [SS_TILE][cols]
-    float* beta_s = v_s + SS_TILE * cols;     // [SS_TILE]
-    float* kq_s = beta_s + SS_TILE;           // [SS_TILE]
+    // two stages of: q [SS_TILE][DP], k [SS_TILE][DP], v [SS_TILE][cols], raw beta and decay
+    // inputs [2][SS_TILE]
+    const int stage_floats = 2 * SS_TILE * DP + SS_TILE * cols + 2 * SS_TILE;
+    __shared__ float beta_s[SS_TILE], kq_s[SS_TILE];
     __shared__ S g_s[SS_TILE];
     const int head = blockIdx.x / chunks_per_head, chunk = blockIdx.x - head * chunks_per_head;
     const int seq = blockIdx.y;
@@ -231,31 +409,56 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
     S s[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = slice + SS_SLICES * i;
+        const int d = row_of(slice, i);
         s[i] = (live && d < dim) ? (S)mine[(int64_t)d * vdim + p] : (S)0;
     }
     const float rate = neg_rate[head], bias = dt_bias[head];
     const float q_scale = 1.f / sqrtf((float)dim);
-    for (int t0 = begin; t0 < end; t0 += SS_TILE) {
+    auto fetch = [&](int stage, int t0) {
+        float* q_to = sm + stage * stage_floats;
+        float* k_to = q_to + SS_TILE * DP;
+        float* v_to = k_to + SS_TILE * DP;
+        float* raw_to = v_to + SS_TILE * cols;
         const int nt = min(SS_TILE, end - t0);
-        __syncthreads();
         for (int idx = tid; idx < nt * DP; idx += blockDim.x) {
             const int tt = idx / DP, d = idx - tt * DP;
             const float* row = qkv + (int64_t)(t0 + tt) * width + kh * dim;
-            q_s[idx] = d < dim ? row[d] : 0.f;
-            k_s[idx] = d < dim ? row[qk + d] : 0.f;
+            const bool take = d < dim;
+            stage_float(q_to + idx, take ? row + d : qkv, take);
+            stage_float(k_to + idx, take ? row + qk + d : qkv, take);
         }
         for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
             const int tt = idx / cols, pl = idx - tt * cols;
             const int pp = chunk * cols + pl;
-            v_s[idx] = pp < vdim ? qkv[(int64_t)(t0 + tt) * width + 2 * qk + head * vdim + pp] : 0.f;
+            const bool take = pp < vdim;
+            stage_float(v_to + idx, take ? qkv + (int64_t)(t0 + tt) * width + 2 * qk + head * vdim + pp : qkv, take);
         }
         if (tid < nt) {
             const float* row = pre + (int64_t)(t0 + tid) * pre_ld;
-            beta_s[tid] = 1.f / (1.f + expf(-row[beta_offset + head]));
-            g_s[tid] = (S)exp((double)rate * softplus_f((double)row[decay_offset + head] + (double)bias));
+            stage_float(raw_to + tid, row + beta_offset + head, true);
+            stage_float(raw_to + SS_TILE + tid, row + decay_offset + head, true);
+        }
+        stage_commit();
+    };
+    fetch(0, begin);
+    int turn = 0;
+    for (int t0 = begin; t0 < end; t0 += SS_TILE, turn ^= 1) {
+        const int nt = min(SS_TILE, end - t0);
+        float* q_s = sm + turn * stage_floats;
+        float* k_s = q_s + SS_TILE * DP;
+        const float* v_s = k_s + SS_TILE * DP;
+        const float* raw_s = v_s + SS_TILE * cols;
+        if (t0 + SS_TILE < end) {
+            fetch(turn ^ 1, t0 + SS_TILE);
+            stage_wait_but_one();
+        } else {
+            stage_wait_all();
         }
         __syncthreads();
+        if (tid < nt) {
+            beta_s[tid] = 1.f / (1.f + expf(-raw_s[tid]));
+            g_s[tid] = (S)exp((double)rate * softplus_f((double)raw_s[SS_TILE + tid] + (double)bias));
+        }
         // unit vectors, and the token's k . q
         for (int tt = warp; tt < nt; tt += warps) {
             float qq = 0.f, kk = 0.f, cross = 0.f;
@@ -277,27 +480,42 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
-            const float* qt = q_s + tt * DP + slice;
-            const float* kt = k_s + tt * DP + slice;
-            S a = (S)0, b = (S)0;
+            const float4* qt = reinterpret_cast<const float4*>(q_s + tt * DP) + slice;
+            const float4* kt = reinterpret_cast<const float4*>(k_s + tt * DP) + slice;
+            float4 kv[DPT / 4];
+            S pa[4] = {(S)0, (S)0, (S)0, (S)0}, pb[4] = {(S)0, (S)0, (S)0, (S)0};
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                a = fma(s[i], (S)kt[SS_SLICES * i], a);
-                b = fma(s[i], (S)qt[SS_SLICES * i], b);
+            for (int j = 0; j < DPT / 4; ++j) {
+                kv[j] = kt[SS_SLICES * j];
+                const float4 qv = qt[SS_SLICES * j];
+                pa[0] = fma(s[4 * j], (S)kv[j].x, pa[0]);
+                pa[1] = fma(s[4 * j + 1], (S)kv[j].y, pa[1]);
+                pa[2] = fma(s[4 * j + 2], (S)kv[j].z, pa[2]);
+                pa[3] = fma(s[4 * j + 3], (S)kv[j].w, pa[3]);
+                pb[0] = fma(s[4 * j], (S)qv.x, pb[0]);
+                pb[1] = fma(s[4 * j + 1], (S)qv.y, pb[1]);
+                pb[2] = fma(s[4 * j + 2], (S)qv.z, pb[2]);
+                pb[3] = fma(s[4 * j + 3], (S)qv.w, pb[3]);
             }
-            a = slice_sum(a);
-            b = slice_sum(b);
+            const S a = slice_sum((pa[0] + pa[1]) + (pa[2] + pa[3]));
+            const S b = slice_sum((pb[0] + pb[1]) + (pb[2] + pb[3]));
             const S g = g_s[tt];
             const S u = (S)beta_s[tt] * ((S)v_s[tt * cols + p_local] - g * a);
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) s[i] = fma(g, s[i], (S)kt[SS_SLICES * i] * u);
+            for (int j = 0; j < DPT / 4; ++j) {
+                s[4 * j] = fma(g, s[4 * j], (S)kv[j].x * u);
+                s[4 * j + 1] = fma(g, s[4 * j + 1], (S)kv[j].y * u);
+                s[4 * j + 2] = fma(g, s[4 * j + 2], (S)kv[j].z * u);
+                s[4 * j + 3] = fma(g, s[4 * j + 3], (S)kv[j].w * u);
+            }
             if (slice == 0 && live)
                 out[(int64_t)(t0 + tt) * inner + head * vdim + p] = (float)fma(u, (S)kq_s[tt], g * b);
         }
+        __syncthreads();                      // the stage may be refilled
     }
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = slice + SS_SLICES * i;
+        const int d = row_of(slice, i);
         if (live && d < dim) mine[(int64_t)d * vdim + p] = (float)s[i];
     }
 }
@@ -366,46 +584,91 @@ MB_EXPORT int mb_conv_tail_update(const float* pre, int ld, int offset, float* t
     return launch_status();
 }
 
-// Warps of a scan block (each holds four columns) and the blocks a head is cut into.
-static void scan_shape(int vdim, int* warps, int* chunks) {
+// Warps of a scan block (each holds four columns) and the blocks a head is cut into. A
+// token costs a warp the same chain of instructions however many warps share its block, so
+// while the blocks are fewer than two to an SM a head is cut into more of them (down to four
+// warps, sixteen columns; fewer warps would spend longer staging a tile's inputs than
+// walking it): the inputs are then staged once per block instead of once per head.
+static void scan_shape(int vdim, int heads, int num_seqs, int* warps, int* chunks) {
     int w = (vdim + 3) / 4;
     if (w > 16) w = 16;
+    while (w > 4 && (long long)heads * ((vdim + 4 * w - 1) / (4 * w)) * num_seqs < 2 * 148) w = (w + 1) / 2;
     *warps = w;
     *chunks = (vdim + 4 * w - 1) / (4 * w);
 }
 
+// A launch that wants more than 48 KB of dynamic shared memory has to say so first (wide
+// matrices only: 256 rows).
+template <typename K>
+static bool allow_smem(K kernel, size_t smem) {
+    return smem <= 48 * 1024 ||
+           cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+}
+
+// Tokens per run when long portions are cut into runs, and the floats of scratch that takes.
+constexpr int SS_RUN = 128;
+
+MB_EXPORT long long mb_mamba2_scratch_floats(int tokens, int num_seqs, int max_q_len, int heads,
+                                            int vdim, int n_state) {
+    const long long runs = (max_q_len + SS_RUN - 1) / SS_RUN;
+    return (long long)num_seqs * runs * heads * ((long long)n_state * vdim + 1) + (long long)tokens * heads;
+}
+
+// `scratch`: null, or mb_mamba2_scratch_floats() floats: with it (and not `precise`) portions
+// of 4 * SS_RUN tokens and more are cut into runs that blocks walk side by side.
 MB_EXPORT int mb_mamba2_scan(const float* xbc, const float* pre, int pre_ld, int dt_offset,
                              const float* dt_bias, const float* neg_rate, const float* skip,
                              float* cells, long long cell_stride, const int* q_start,
-                             const int* slots, float* y, int num_seqs, int heads, int vdim,
-                             int n_state, int groups, int precise, void* stream) {
+                             const int* slots, float* y, int tokens, int num_seqs, int max_q_len,
+                             int heads, int vdim, int n_state, int groups, int precise,
+                             float* scratch, void* stream) {
     if (num_seqs <= 0) return MB_OK;
     if (heads <= 0 || vdim <= 0 || n_state <= 0 || n_state > 256 || groups <= 0 || heads % groups ||
         num_seqs > 65535)
         return MB_ERR_UNSUPPORTED_SIZE;
+    const bool in_runs = scratch != nullptr && !precise && max_q_len >= 4 * SS_RUN;
+    const int max_runs = in_runs ? (max_q_len + SS_RUN - 1) / SS_RUN : 1;
+    if (max_runs > 65535) return MB_ERR_UNSUPPORTED_SIZE;
     int warps, chunks;
-    scan_shape(vdim, &warps, &chunks);
-    dim3 grid(heads * chunks, num_seqs);
+    scan_shape(vdim, heads, num_seqs * max_runs, &warps, &chunks);
+    dim3 grid(heads * chunks, num_seqs, max_runs);
     cudaStream_t s = (cudaStream_t)stream;
+    const int per_head = n_state * vdim;
+    float* run_end = scratch;
+    float* run_decay = in_runs ? run_end + (int64_t)num_seqs * max_runs * heads * per_head : nullptr;
+    float* cum = in_runs ? run_decay + (int64_t)num_seqs * max_runs * heads : nullptr;
+#define MB_M2_ARGS xbc, pre, pre_ld, dt_offset, dt_bias, neg_rate, skip, cells, (int64_t)cell_stride, \
+                   q_start, slots, y, heads, vdim, n_state, groups, chunks, SS_RUN, run_end, run_decay, cum
 #define MB_M2_CASE(NPT)                                                                            \
     do {                                                                                           \
-        const size_t smem = (size_t)(2 * SS_TILE * NPT * SS_SLICES + SS_TILE * warps * 4) *        \
-                            sizeof(float);                                                         \
+        const size_t smem = (size_t)2 * (2 * SS_TILE * NPT * SS_SLICES + SS_TILE * warps * 4 +      \
+                                         SS_TILE) * sizeof(float);                                 \
+        if (!allow_smem(mamba2_scan_kernel<NPT, double, false>, smem) ||                           \
+            !allow_smem(mamba2_scan_kernel<NPT, float, false>, smem) ||                            \
+            !allow_smem(mamba2_scan_kernel<NPT, float, true>, smem))                               \
+            return MB_ERR_UNSUPPORTED_SIZE;                                                        \
         if (precise)                                                                               \
-            MB_LAUNCH((mamba2_scan_kernel<NPT, double>), grid, warps * 32, smem, s, xbc, pre, pre_ld,  \
-                      dt_offset, dt_bias, neg_rate, skip, cells, (int64_t)cell_stride, q_start,    \
-                      slots, y, heads, vdim, n_state, groups, chunks);                             \
-        else                                                                                       \
-            MB_LAUNCH((mamba2_scan_kernel<NPT, float>), grid, warps * 32, smem, s, xbc, pre, pre_ld,   \
-                      dt_offset, dt_bias, neg_rate, skip, cells, (int64_t)cell_stride, q_start,    \
-                      slots, y, heads, vdim, n_state, groups, chunks);                             \
+            MB_LAUNCH((mamba2_scan_kernel<NPT, double, false>), grid, warps * 32, smem, s, MB_M2_ARGS); \
+        else if (!in_runs)                                                                         \
+            MB_LAUNCH((mamba2_scan_kernel<NPT, float, false>), grid, warps * 32, smem, s, MB_M2_ARGS);  \
+        else {                                                                                     \
+            MB_LAUNCH((mamba2_scan_kernel<NPT, float, true>), grid, warps * 32, smem, s, MB_M2_ARGS);   \
+            dim3 cgrid((heads * per_head + 255) / 256, num_seqs);                                  \
+            MB_LAUNCH((mamba2_carry_kernel), cgrid, 256, 0, s, run_end, run_decay, cells,          \
+                      (int64_t)cell_stride, q_start, slots, heads, per_head, SS_RUN, max_runs);    \
+            const size_t asmem = (size_t)2 * (SS_TILE * NPT * SS_SLICES + SS_TILE) * sizeof(float); \
+            if (!allow_smem(mamba2_apply_kernel<NPT>, asmem)) return MB_ERR_UNSUPPORTED_SIZE;      \
+            MB_LAUNCH((mamba2_apply_kernel<NPT>), grid, warps * 32, asmem, s, xbc, run_end, cum,   \
+                      q_start, y, heads, vdim, n_state, groups, chunks, SS_RUN);                   \
+        }                                                                                          \
     } while (0)
-    if (n_state <= 16) MB_M2_CASE(2);
-    else if (n_state <= 32) MB_M2_CASE(4);
+    if (n_state <= 32) MB_M2_CASE(4);
     else if (n_state <= 64) MB_M2_CASE(8);
     else if (n_state <= 128) MB_M2_CASE(16);
     else MB_M2_CASE(32);
 #undef MB_M2_CASE
+#undef MB_M2_ARGS
+    (void)tokens;
     return launch_status();
 }
 
@@ -420,13 +683,16 @@ MB_EXPORT int mb_delta_rule_scan(const float* qkv, const float* pre, int pre_ld,
         num_seqs > 65535)
         return MB_ERR_UNSUPPORTED_SIZE;
     int warps, chunks;
-    scan_shape(vdim, &warps, &chunks);
+    scan_shape(vdim, heads, num_seqs, &warps, &chunks);
     dim3 grid(heads * chunks, num_seqs);
     cudaStream_t s = (cudaStream_t)stream;
 #define MB_DR_CASE(DPT)                                                                            \
     do {                                                                                           \
-        const size_t smem = (size_t)(2 * SS_TILE * DPT * SS_SLICES + SS_TILE * warps * 4 +         \
-                                     2 * SS_TILE) * sizeof(float);                                 \
+        const size_t smem = (size_t)2 * (2 * SS_TILE * DPT * SS_SLICES + SS_TILE * warps * 4 +      \
+                                         2 * SS_TILE) * sizeof(float);                             \
+        if (!allow_smem(delta_rule_scan_kernel<DPT, double>, smem) ||                              \
+            !allow_smem(delta_rule_scan_kernel<DPT, float>, smem))                                 \
+            return MB_ERR_UNSUPPORTED_SIZE;                                                        \
         if (precise)                                                                               \
             MB_LAUNCH((delta_rule_scan_kernel<DPT, double>), grid, warps * 32, smem, s, qkv, pre,  \
                       pre_ld, beta_offset, decay_offset, dt_bias, neg_rate, unit_eps, cells,       \
@@ -438,8 +704,7 @@ MB_EXPORT int mb_delta_rule_scan(const float* qkv, const float* pre, int pre_ld,
                       (int64_t)cell_stride, q_start, slots, out, heads, key_heads, dim, vdim,      \
                       chunks);                                                                     \
     } while (0)
-    if (dim <= 16) MB_DR_CASE(2);
-    else if (dim <= 32) MB_DR_CASE(4);
+    if (dim <= 32) MB_DR_CASE(4);
     else if (dim <= 64) MB_DR_CASE(8);
     else if (dim <= 128) MB_DR_CASE(16);
     else MB_DR_CASE(32);

@@ -121,7 +121,7 @@ _SIGNATURES = {
                             c_int, c_int, c_void_p],
     "mb_mamba2_scan": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                       c_int, c_void_p],
+                       c_int, c_int, c_int, c_void_p, c_void_p],
     "mb_delta_rule_scan": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
                            c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_void_p],
@@ -131,12 +131,13 @@ _SIGNATURES = {
                              c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "mb_head_linear": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                        c_int, c_int, c_void_p],
-    "mb_route_experts": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                         c_int, c_int, c_int, c_float, c_void_p],
-    "mb_expert_tile_cap": [c_int, c_int],
-    "mb_expert_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "mb_route_experts": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                         c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "mb_expert_tile_rows": [c_int, c_int, c_int],
+    "mb_expert_tile_cap": [c_int, c_int, c_int],
+    "mb_expert_plan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "mb_expert_product": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                          c_int, c_int, c_void_p],
+                          c_int, c_int, c_int, c_void_p],
     "mb_expert_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "mb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -183,6 +184,8 @@ def load():
     lib.mb_mixed_head_mma_supports.restype = c_int
     lib.mb_mixed_head_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mb_mixed_head_scratch_floats.restype = c_longlong
+    lib.mb_mamba2_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int]
+    lib.mb_mamba2_scratch_floats.restype = c_longlong
     _LIB = lib
     return lib
 

@@ -103,6 +103,9 @@ class CudaOps:
         self.attention = "auto"
         # the mixed-head attention: "auto" (tensor cores where they take the sizes) or "simt"
         self.mixed_head = "auto"
+        # the grouped products of routed experts: mma.sync where the sizes allow (bfloat16,
+        # widths in multiples of 8); False leaves them to the CUDA-core kernel
+        self.expert_tensor_cores = True
         self.mixed_head_blocks_per_sm = 4
         self.mixed_head_max_splits = 32
         self.prompt_cluster: int | None = None  # override of the CTAs per row tile (1, 2, 4)
@@ -155,6 +158,12 @@ class CudaOps:
         self._tc_error: torch.Tensor | None = None   # error word of the tcgen05 kernels
         self._tc_pending = False
         self._argmax_scratch: torch.Tensor | None = None
+        self._router_logits: torch.Tensor | None = None
+        self._scan_scratch: torch.Tensor | None = None
+        # the state-space scan of a long portion in runs walked side by side (from 512 tokens on:
+        # below that the sequential walk is as fast and is one launch)
+        self.scan_runs = True
+        self.scan_runs_min_tokens = 512
         self._float_biases: dict = {}
         self._timing: list | None = None      # (kind, start event, stop event) while timing
         self._timing_depth = 0
@@ -233,6 +242,14 @@ class CudaOps:
             self._scratch = torch.empty(max(floats, 1 << 20), dtype=torch.float32,
                                         device=self.device)
         return self._scratch
+
+    def _scan_scratch_for(self, floats: int) -> torch.Tensor:
+        if self._scan_scratch is None or self._scan_scratch.numel() < floats:
+            if self._scan_scratch is not None:
+                self._retired.append(self._scan_scratch)
+            self._scan_scratch = torch.empty(max(floats, 1 << 20), dtype=torch.float32,
+                                             device=self.device)
+        return self._scan_scratch
 
     def _counters_for(self, count: int) -> torch.Tensor:
         """Zeroed tickets of the in-kernel split merge (the last block resets its own)."""
@@ -654,12 +671,19 @@ class CudaOps:
         is a view of the state rows; everything float32. `precise`: the matrices are held in
         double while the step runs (the float32 engine; see csrc/state_space.cu)."""
         heads, vdim, n_state, groups = layout
+        tokens = xbc.shape[0]
+        # long portions are cut into runs that blocks walk side by side (three launches)
+        in_runs = self.scan_runs and not precise and batch.max_q_len >= self.scan_runs_min_tokens
+        scratch = None
+        if in_runs:
+            scratch = self._scan_scratch_for(self.lib.mb_mamba2_scratch_floats(
+                tokens, batch.num_seqs, batch.max_q_len, heads, vdim, n_state))
         check(self.lib.mb_mamba2_scan(
             _ptr(xbc), _ptr(pre), pre.shape[1], int(dt_offset), _ptr(dt_bias), _ptr(neg_rate),
             _ptr(skip), _ptr(cells), cells.stride(0), _ptr(batch.q_start), _ptr(batch.slots), _ptr(y),
-            batch.num_seqs, heads, vdim, n_state, groups, int(bool(precise)), self._stream()),
-            "mamba2_scan")
-        self.launches += 1
+            tokens, batch.num_seqs, batch.max_q_len, heads, vdim, n_state, groups,
+            int(bool(precise)), _ptr(scratch), self._stream()), "mamba2_scan")
+        self.launches += 3 if in_runs else 1
 
     @_timed("recurrence")
     def delta_rule_scan(self, qkv, pre, beta_offset, decay_offset, dt_bias, neg_rate, layout,
@@ -720,11 +744,17 @@ class CudaOps:
         if self._pending(x) is not None:
             x = x.materialize()
         tokens, top = chosen.shape
+        experts = router.shape[0]
+        if self._router_logits is None or self._router_logits.numel() < tokens * experts:
+            if self._router_logits is not None:
+                self._retired.append(self._router_logits)    # captured graphs still write there
+            self._router_logits = torch.empty(max(tokens * experts, 1 << 16), dtype=torch.float32,
+                                              device=self.device)
         check(self.lib.mb_route_experts(
-            _ptr(x), _flag(x.dtype), _ptr(router), _ptr(correction), _ptr(chosen), _ptr(weights),
-            tokens, x.shape[1], router.shape[0], top, int(group_count), int(group_keep),
-            float(route_scale), self._stream()), "route_experts")
-        self.launches += 1
+            _ptr(x), _flag(x.dtype), _ptr(router), _ptr(correction), _ptr(self._router_logits),
+            _ptr(chosen), _ptr(weights), tokens, x.shape[1], experts, top, int(group_count),
+            int(group_keep), float(route_scale), self._stream()), "route_experts")
+        self.launches += 2
 
     @_timed("expert products")
     def expert_feed_forward(self, x, chosen, weights, gate_up, down, out, ctx):
@@ -737,19 +767,21 @@ class CudaOps:
         experts, _two_ff, hidden = gate_up.shape
         ff = down.shape[2]
         pairs = tokens * top
-        cap = self.lib.mb_expert_tile_cap(pairs, experts)
+        # rows per tile: 64 on the tensor cores (bfloat16, sizes in multiples of 8), else 32
+        bm = self.lib.mb_expert_tile_rows(_flag(x.dtype), hidden, ff) if self.expert_tensor_cores else 32
+        cap = self.lib.mb_expert_tile_cap(pairs, experts, bm)
         plan = ctx.buffer("expert_plan", 1 + 3 * cap + pairs, 1, dtype=torch.int32)
-        check(self.lib.mb_expert_plan(_ptr(chosen), pairs, experts, cap, _ptr(plan), self._stream()),
-              "expert_plan")
+        check(self.lib.mb_expert_plan(_ptr(chosen), pairs, experts, cap, bm, _ptr(plan),
+                                      self._stream()), "expert_plan")
         act = ctx.buffer("expert_act", pairs, ff)
         if act.dtype != x.dtype or gate_up.dtype != x.dtype or down.dtype != x.dtype:
             raise KernelError("expert_feed_forward: activations and expert matrices differ in dtype")
         check(self.lib.mb_expert_product(0, _ptr(x), x.shape[1], _ptr(gate_up), _ptr(act), _ptr(plan),
-                                         cap, top, hidden, ff, _flag(x.dtype), self._stream()),
+                                         cap, top, hidden, ff, _flag(x.dtype), bm, self._stream()),
               "expert gate/up product")
         y = ctx.buffer("expert_rows", pairs, hidden, dtype="float32")
         check(self.lib.mb_expert_product(1, _ptr(act), ff, _ptr(down), _ptr(y), _ptr(plan), cap, top,
-                                         ff, hidden, _flag(x.dtype), self._stream()),
+                                         ff, hidden, _flag(x.dtype), bm, self._stream()),
               "expert down product")
         check(self.lib.mb_expert_combine(_ptr(y), _ptr(weights), _ptr(out), tokens, top, hidden,
                                          self._stream()), "expert_combine")

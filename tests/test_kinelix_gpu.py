@@ -162,6 +162,40 @@ def test_convolution_and_mamba2_over_steps(ops, twin, precise, heads, vdim, n, g
     assert not state[0].any() and not state[2].any() and not state[4].any()
 
 
+@pytest.mark.parametrize("heads,vdim,n,groups", [(4, 16, 24, 2), (6, 64, 128, 3), (2, 40, 16, 1)])
+def test_mamba2_long_portions_in_runs(ops, twin, heads, vdim, n, groups):
+    """Portions long enough to be cut into runs that blocks walk side by side (a run that is
+    full, one that is not, a sequence shorter than a run beside them), from a state that an
+    earlier step left, against the sequential walk and the twin."""
+    inner = heads * vdim
+    channels = inner + 2 * groups * n
+    proj = 2 * inner + 2 * groups * n + heads
+    cells = heads * n * vdim
+    dt_bias, rate = rand((heads,), torch.float32, 22) - 3.0, -torch.exp(rand((heads,), torch.float32, 23, 0.5))
+    skip = rand((heads,), torch.float32, 24) + 1
+    states = [rand((4, cells), torch.float32, 25, 0.5) for _ in range(3)]
+    outs = []
+    for step, q_lens in enumerate([(700, 3, 129), (1, 513, 2)]):
+        batch = ragged(q_lens, slots=[2, 0, 3], pad=1)
+        tokens = batch.num_tokens
+        pre = rand((tokens, proj), torch.float32, 30 + step)
+        xbc = rand((tokens, channels), torch.float32, 40 + step, 0.5)
+        row = []
+        for which, st, runs in ((ops, states[0], True), (ops, states[1], False), (twin, states[2], None)):
+            if runs is not None:
+                ops.scan_runs = runs
+            y = torch.zeros((tokens, inner), dtype=torch.float32, device="cuda")
+            which.mamba2_scan(xbc, pre, proj - heads, dt_bias, rate, skip, (heads, vdim, n, groups), st,
+                              batch, y)
+            row.append(y)
+        ops.scan_runs = True
+        live = batch.seq_of_token >= 0
+        close(row[0][live], row[2][live], torch.float32, f"in runs, step {step}", 2e-5)
+        close(row[1][live], row[2][live], torch.float32, f"sequential, step {step}", 2e-5)
+        close(states[0], states[2], torch.float32, f"state in runs, step {step}", 2e-5)
+        close(states[1], states[2], torch.float32, f"state, step {step}", 2e-5)
+
+
 @pytest.mark.parametrize("precise", [False, True], ids=["float", "double"])
 @pytest.mark.parametrize("heads,key_heads,dim,vdim,taps", [(4, 2, 24, 16, 3), (3, 3, 16, 32, 1), (6, 3, 20, 12, 5),
                                                            (2, 1, 130, 72, 2), (8, 4, 128, 128, 4)])

@@ -141,7 +141,9 @@ __global__ void route_select_kernel(const float* __restrict__ logits,
 
 // One block sorts the step's pairs by expert. plan: [0] tiles in all, then tile_expert[cap],
 // tile_row0[cap], tile_rows[cap], then perm[pairs] (pair = token * top + choice, grouped by
-// expert; the order inside an expert is arbitrary and changes no result).
+// expert; the order inside an expert is arbitrary and changes no result), then ends[experts]
+// (where each expert's rows end in the sorted order) and place[pairs] (the sorted row of
+// every pair): what a library's grouped product and the sum behind it need.
 __global__ void __launch_bounds__(1024)
 expert_plan_kernel(const int* __restrict__ chosen, int pairs, int experts, int cap, int bm,
                    int* __restrict__ plan) {
@@ -160,6 +162,8 @@ expert_plan_kernel(const int* __restrict__ chosen, int pairs, int experts, int c
     int* tile_row0 = tile_expert + cap;
     int* tile_rows = tile_row0 + cap;
     int* perm = tile_rows + cap;
+    int* ends = perm + pairs;
+    int* place = ends + experts;
     if (threadIdx.x == 0) {
         int at = 0, tiles = 0;
         for (int e = 0; e < experts; ++e) {
@@ -171,13 +175,56 @@ expert_plan_kernel(const int* __restrict__ chosen, int pairs, int experts, int c
                 ++tiles;
             }
             at += count_s[e];
+            ends[e] = at;
         }
         plan[0] = tiles;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
         const int e = chosen[i];
-        if (e >= 0 && e < experts) perm[atomicAdd(&start_s[e], 1)] = i;
+        if (e >= 0 && e < experts) {
+            const int at = atomicAdd(&start_s[e], 1);
+            perm[at] = i;
+            place[i] = at;
+        }
+    }
+}
+
+// sorted[i][:] = x[perm[i] / top][:]: the tokens' rows in the order of the plan, 16 bytes a
+// thread (hidden a multiple of 8).
+__global__ void expert_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ perm,
+                                     __nv_bfloat16* __restrict__ sorted, int pairs, int top,
+                                     int hidden) {
+    grid_dependency_sync();
+    const int chunks = hidden / 8;
+    const int64_t total = (int64_t)pairs * chunks;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / chunks;
+        const int c = (int)(i - r * chunks);
+        const int t = perm[r] / top;
+        reinterpret_cast<uint4*>(sorted + r * hidden)[c] =
+            reinterpret_cast<const uint4*>(x + (int64_t)t * hidden)[c];
+    }
+}
+
+// out[t][n] = sum_j weights[t][j] * y[place[t * top + j]][n], j ascending: the weighted sum
+// over rows that lie in the plan's order.
+__global__ void expert_combine_sorted_kernel(const __nv_bfloat16* __restrict__ y,
+                                             const int* __restrict__ place,
+                                             const float* __restrict__ weights, float* __restrict__ out,
+                                             int tokens, int top, int hidden) {
+    grid_dependency_sync();
+    const int64_t total = (int64_t)tokens * hidden;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / hidden;
+        const int n = (int)(i - t * hidden);
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j)
+            acc = fmaf(weights[t * top + j],
+                       __bfloat162float(y[(int64_t)place[t * top + j] * hidden + n]), acc);
+        out[i] = acc;
     }
 }
 
@@ -281,14 +328,15 @@ expert_product_kernel(const TA* __restrict__ a, int a_ld, const TW* __restrict__
 
 
 // ---- the same products on the tensor cores (bfloat16) --------------------------------------
-// mma.sync m16n8k16 with float32 accumulators. A block of four warps takes a tile of TC_BM
+// mma.sync m16n8k16 with float32 accumulators. A block of eight warps takes a tile of TC_BM
 // rows of one expert and TC_BN output columns (in MODE 0 the TC_BN gate rows and the TC_BN up
-// rows of the matrix that belong to them), K in rounds of TC_BK through two shared-memory
+// rows of the matrix that belong to them), K in rounds of TC_BK through three shared-memory
 // stages filled by 16-byte cp.async (rows of 128 bytes, the 16-byte pieces of a row permuted
-// by the row's low bits so that ldmatrix meets no bank twice). Rows beyond the tile, columns
-// beyond N and pieces beyond K are filled with zeros by the copy itself. A row's sums do not
-// depend on the other rows of its tile.
-constexpr int TC_BM = 64, TC_BN = 64, TC_BK = 64;
+// by the row's low bits so that ldmatrix meets no bank twice). The warps lie 4 x 2: a warp
+// owns 32 rows and 32 columns (of both parts), so a fragment of the matrix serves two row
+// tiles. Rows beyond the tile, columns beyond N and pieces beyond K are filled with zeros by
+// the copy itself. A row's sums do not depend on the other rows of its tile.
+constexpr int TC_BM = 128, TC_BN = 64, TC_BK = 64, TC_STAGES = 3, TC_THREADS = 256;
 
 __device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool full) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -311,7 +359,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(TC_THREADS)
 expert_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_ld,
                           const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
                           const int* __restrict__ plan, int cap, int top, int K, int N) {
@@ -327,10 +375,11 @@ expert_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_ld,
     constexpr int PARTS = MODE == 0 ? 2 : 1;
     constexpr int W_ROWS = PARTS * TC_BN;
     extern __shared__ __align__(128) unsigned char tc_smem[];
-    __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(tc_smem);            // [2][TC_BM][TC_BK]
-    __nv_bfloat16* w_s = a_s + 2 * TC_BM * TC_BK;                               // [2][W_ROWS][TC_BK]
+    __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(tc_smem);            // [stages][TC_BM][TC_BK]
+    __nv_bfloat16* w_s = a_s + TC_STAGES * TC_BM * TC_BK;                       // [stages][W_ROWS][TC_BK]
     __shared__ int src_s[TC_BM];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wr = warp >> 1, wc = warp & 1;
     if (tid < TC_BM) {
         int src = -1;
         if (tid < rows) src = MODE == 0 ? perm[row0 + tid] / top : row0 + tid;
@@ -338,99 +387,111 @@ expert_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_ld,
     }
     __syncthreads();
     const __nv_bfloat16* we = w + (int64_t)e * (PARTS * N) * K;
+    const int rounds = (K + TC_BK - 1) / TC_BK;
 
-    auto fill = [&](int stage, int k0) {
-        // A: TC_BM rows x 8 pieces
-        for (int idx = tid; idx < TC_BM * 8; idx += 128) {
-            const int r = idx >> 3, c = idx & 7;
-            const int src = src_s[r];
-            const bool ok = src >= 0 && k0 + c * 8 < K;
-            const __nv_bfloat16* from = ok ? a + (int64_t)src * a_ld + k0 + c * 8 : a;
-            cp_async_16(a_s + (stage * TC_BM + r) * TC_BK + ((c ^ (r & 7)) * 8), from, ok);
-        }
-        for (int idx = tid; idx < W_ROWS * 8; idx += 128) {
-            const int r = idx >> 3, c = idx & 7;
-            const int part = r / TC_BN, n = n0 + (r - part * TC_BN);
-            const bool ok = n < N && k0 + c * 8 < K;
-            const __nv_bfloat16* from = ok ? we + (int64_t)(part * N + n) * K + k0 + c * 8 : w;
-            cp_async_16(w_s + (stage * W_ROWS + r) * TC_BK + ((c ^ (r & 7)) * 8), from, ok);
+    // every call commits a group, an empty one beyond the last round, so that the count of
+    // groups in flight tells which round has landed
+    auto fill = [&](int round) {
+        if (round < rounds) {
+            const int stage = round % TC_STAGES, k0 = round * TC_BK;
+            for (int idx = tid; idx < TC_BM * 8; idx += TC_THREADS) {
+                const int r = idx >> 3, c = idx & 7;
+                const int src = src_s[r];
+                const bool ok = src >= 0 && k0 + c * 8 < K;
+                const __nv_bfloat16* from = ok ? a + (int64_t)src * a_ld + k0 + c * 8 : a;
+                cp_async_16(a_s + (stage * TC_BM + r) * TC_BK + ((c ^ (r & 7)) * 8), from, ok);
+            }
+            for (int idx = tid; idx < W_ROWS * 8; idx += TC_THREADS) {
+                const int r = idx >> 3, c = idx & 7;
+                const int part = r / TC_BN, n = n0 + (r - part * TC_BN);
+                const bool ok = n < N && k0 + c * 8 < K;
+                const __nv_bfloat16* from = ok ? we + (int64_t)(part * N + n) * K + k0 + c * 8 : w;
+                cp_async_16(w_s + (stage * W_ROWS + r) * TC_BK + ((c ^ (r & 7)) * 8), from, ok);
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
-    float acc[PARTS][TC_BN / 8][4];
+    // acc[part][row tile of 16][column tile of 8][4]
+    float acc[PARTS][2][4][4];
 #pragma unroll
     for (int p = 0; p < PARTS; ++p)
 #pragma unroll
-        for (int j = 0; j < TC_BN / 8; ++j)
+        for (int i = 0; i < 2; ++i)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) acc[p][j][c] = 0.f;
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[p][i][j][c] = 0.f;
 
-    const int rounds = (K + TC_BK - 1) / TC_BK;
-    fill(0, 0);
+#pragma unroll
+    for (int st = 0; st < TC_STAGES - 1; ++st) fill(st);
     for (int kt = 0; kt < rounds; ++kt) {
-        if (kt + 1 < rounds) {
-            fill((kt + 1) & 1, (kt + 1) * TC_BK);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
-        __syncthreads();
-        const __nv_bfloat16* as = a_s + ((kt & 1) * TC_BM + warp * 16) * TC_BK;
-        const __nv_bfloat16* ws = w_s + (kt & 1) * W_ROWS * TC_BK;
+        asm volatile("cp.async.wait_group %0;" ::"n"(TC_STAGES - 2) : "memory");
+        __syncthreads();        // round kt has landed for everyone, and round kt - 1 is consumed
+        fill(kt + TC_STAGES - 1);
+        const int stage = kt % TC_STAGES;
+        const __nv_bfloat16* as = a_s + (stage * TC_BM + wr * 32) * TC_BK;
+        const __nv_bfloat16* ws = w_s + stage * W_ROWS * TC_BK;
 #pragma unroll
         for (int kk = 0; kk < TC_BK / 16; ++kk) {
-            uint32_t af[4];
-            {
-                const int r = lane & 15, c = kk * 2 + (lane >> 4);
-                ldmatrix_x4(af, as + r * TC_BK + ((c ^ (r & 7)) * 8));
+            uint32_t af[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = i * 16 + (lane & 15), c = kk * 2 + (lane >> 4);
+                ldmatrix_x4(af[i], as + r * TC_BK + ((c ^ (r & 7)) * 8));
             }
 #pragma unroll
             for (int p = 0; p < PARTS; ++p) {
 #pragma unroll
-                for (int j2 = 0; j2 < TC_BN / 16; ++j2) {
+                for (int j2 = 0; j2 < 2; ++j2) {
                     // two column tiles of 8 at once: lanes 0-15 the first (its two k halves),
                     // lanes 16-31 the second
                     uint32_t bf[4];
-                    const int r = p * TC_BN + j2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+                    const int r = p * TC_BN + wc * 32 + j2 * 16 + (lane & 7) + ((lane >> 4) << 3);
                     const int c = kk * 2 + ((lane >> 3) & 1);
                     ldmatrix_x4(bf, ws + r * TC_BK + ((c ^ (r & 7)) * 8));
-                    mma_bf16_16816(acc[p][2 * j2], af, bf[0], bf[1]);
-                    mma_bf16_16816(acc[p][2 * j2 + 1], af, bf[2], bf[3]);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        mma_bf16_16816(acc[p][i][2 * j2], af[i], bf[0], bf[1]);
+                        mma_bf16_16816(acc[p][i][2 * j2 + 1], af[i], bf[2], bf[3]);
+                    }
                 }
             }
         }
-        __syncthreads();       // the stage is free before the round after next refills it
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int lr = warp * 16 + g + h * 8;
-        if (lr >= rows) continue;
-        const int64_t dst_row = MODE == 0 ? (int64_t)(row0 + lr) : (int64_t)perm[row0 + lr];
+    for (int i = 0; i < 2; ++i) {
 #pragma unroll
-        for (int j = 0; j < TC_BN / 8; ++j) {
-            const int n = n0 + j * 8 + 2 * t4;
-            if (n >= N) continue;
-            const float v0 = acc[0][j][2 * h], v1 = acc[0][j][2 * h + 1];
-            if (MODE == 0) {
-                const float u0 = acc[PARTS - 1][j][2 * h], u1 = acc[PARTS - 1][j][2 * h + 1];
-                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + dst_row * N + n;
-                const float r0 = v0 / (1.f + expf(-v0)) * u0, r1 = v1 / (1.f + expf(-v1)) * u1;
-                if (n + 1 < N && (N & 1) == 0)
-                    *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(r0, r1);
-                else {
-                    o[0] = __float2bfloat16_rn(r0);
-                    if (n + 1 < N) o[1] = __float2bfloat16_rn(r1);
-                }
-            } else {
-                float* o = reinterpret_cast<float*>(out) + dst_row * N + n;
-                if (n + 1 < N && (N & 1) == 0)
-                    *reinterpret_cast<float2*>(o) = make_float2(v0, v1);
-                else {
-                    o[0] = v0;
-                    if (n + 1 < N) o[1] = v1;
+        for (int h = 0; h < 2; ++h) {
+            const int lr = wr * 32 + i * 16 + g + h * 8;
+            if (lr >= rows) continue;
+            const int64_t dst_row = MODE == 0 ? (int64_t)(row0 + lr) : (int64_t)perm[row0 + lr];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = n0 + wc * 32 + j * 8 + 2 * t4;
+                if (n >= N) continue;
+                const float v0 = acc[0][i][j][2 * h], v1 = acc[0][i][j][2 * h + 1];
+                if (MODE == 0) {
+                    const float u0 = acc[PARTS - 1][i][j][2 * h], u1 = acc[PARTS - 1][i][j][2 * h + 1];
+                    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + dst_row * N + n;
+                    const float r0 = v0 / (1.f + expf(-v0)) * u0, r1 = v1 / (1.f + expf(-v1)) * u1;
+                    if (n + 1 < N && (N & 1) == 0)
+                        *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(r0, r1);
+                    else {
+                        o[0] = __float2bfloat16_rn(r0);
+                        if (n + 1 < N) o[1] = __float2bfloat16_rn(r1);
+                    }
+                } else {
+                    float* o = reinterpret_cast<float*>(out) + dst_row * N + n;
+                    if (n + 1 < N && (N & 1) == 0)
+                        *reinterpret_cast<float2*>(o) = make_float2(v0, v1);
+                    else {
+                        o[0] = v0;
+                        if (n + 1 < N) o[1] = v1;
+                    }
                 }
             }
         }
@@ -441,7 +502,7 @@ template <int MODE>
 int launch_expert_product_mma(const void* a, int a_ld, const void* w, void* out, const int* plan,
                               int cap, int top, int K, int N, cudaStream_t s) {
     constexpr int PARTS = MODE == 0 ? 2 : 1;
-    const size_t smem = (size_t)2 * (TC_BM + PARTS * TC_BN) * TC_BK * sizeof(__nv_bfloat16);
+    const size_t smem = (size_t)TC_STAGES * (TC_BM + PARTS * TC_BN) * TC_BK * sizeof(__nv_bfloat16);
     // (with the kernel's static shared memory this is beyond the 48 KB a launch gets unasked)
     static bool raised = false;
     if (!raised) {
@@ -452,7 +513,7 @@ int launch_expert_product_mma(const void* a, int a_ld, const void* w, void* out,
     }
     dim3 grid(cap, (N + TC_BN - 1) / TC_BN);
     if (grid.y > 65535) return MB_ERR_UNSUPPORTED_SIZE;
-    MB_LAUNCH((expert_product_mma_kernel<MODE>), grid, 128, smem, s, (const __nv_bfloat16*)a, a_ld,
+    MB_LAUNCH((expert_product_mma_kernel<MODE>), grid, TC_THREADS, smem, s, (const __nv_bfloat16*)a, a_ld,
               (const __nv_bfloat16*)w, out, plan, cap, top, K, N);
     return launch_status();
 }
@@ -530,7 +591,7 @@ MB_EXPORT int mb_route_experts(const void* x, int x_dtype, const float* router,
 }
 
 // Rows per tile of the grouped products for this dtype and these sizes: the tensor-core
-// kernel (bfloat16, K a multiple of 8 in both products) takes tiles of 64, the CUDA-core
+// kernel (bfloat16, K a multiple of 8 in both products) takes tiles of 128, the CUDA-core
 // kernel tiles of 32.
 MB_EXPORT int mb_expert_tile_rows(int dtype, int hidden, int ff) {
     return (dtype == MB_BF16 && hidden % 8 == 0 && ff % 8 == 0) ? TC_BM : EX_BM;
@@ -542,7 +603,7 @@ MB_EXPORT int mb_expert_tile_cap(int pairs, int experts, int bm) {
     return pairs < bound ? pairs : bound;
 }
 
-// Integers the plan needs: 1 + 3 * cap + pairs.
+// Integers the plan needs: 1 + 3 * cap + 2 * pairs + experts.
 MB_EXPORT int mb_expert_plan(const int* chosen, int pairs, int experts, int cap, int bm, int* plan,
                              void* stream) {
     if (pairs <= 0) return MB_OK;
@@ -574,6 +635,28 @@ MB_EXPORT int mb_expert_product(int mode, const void* a, int a_ld, const void* w
         return launch_expert_product<__nv_bfloat16, __nv_bfloat16>(mode, a, a_ld, w, out, plan, cap, top,
                                                                    K, N, s);
     return MB_ERR_BAD_DTYPE;
+}
+
+MB_EXPORT int mb_expert_gather(const void* x, const int* perm, void* sorted, int pairs, int top,
+                               int hidden, void* stream) {
+    if (pairs <= 0) return MB_OK;
+    if (hidden % 8 || (((uintptr_t)x | (uintptr_t)sorted) & 15)) return MB_ERR_ALIGNMENT;
+    const long long want = ((long long)pairs * (hidden / 8) + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    MB_LAUNCH((expert_gather_kernel), blocks, 256, 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, perm,
+              (__nv_bfloat16*)sorted, pairs, top, hidden);
+    return launch_status();
+}
+
+MB_EXPORT int mb_expert_combine_sorted(const void* y, const int* place, const float* weights,
+                                       float* out, int tokens, int top, int hidden, void* stream) {
+    const long long total = (long long)tokens * hidden;
+    if (total <= 0) return MB_OK;
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+    MB_LAUNCH((expert_combine_sorted_kernel), blocks, 256, 0, (cudaStream_t)stream,
+              (const __nv_bfloat16*)y, place, weights, out, tokens, top, hidden);
+    return launch_status();
 }
 
 MB_EXPORT int mb_expert_combine(const float* y, const float* weights, float* out, int tokens,

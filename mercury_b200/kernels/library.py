@@ -138,6 +138,8 @@ _SIGNATURES = {
     "mb_expert_plan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "mb_expert_product": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_void_p],
+    "mb_expert_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "mb_expert_combine_sorted": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_expert_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "mb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],

@@ -415,7 +415,7 @@ def test_the_correction_steers_the_choice_only(ops):
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("tokens,hidden,ff,experts,top", [(1, 64, 40, 8, 2), (37, 100, 34, 6, 3),
                                                           (300, 256, 96, 16, 4), (70, 48, 130, 2, 2),
-                                                          (9, 136, 64, 5, 1)])
+                                                          (9, 136, 64, 5, 1), (700, 128, 72, 12, 3)])
 def test_expert_products(ops, twin, dtype, tokens, hidden, ff, experts, top):
     """Experts that get many rows, one row and none; sizes that fill no tile."""
     x = rand((tokens, hidden), dtype, 140)

@@ -61,7 +61,7 @@ RAW = {
         _layer("mamba2", _mamba(4, 16, 24, 2, 2, 4), _moe(40, 6, 2, count=3, keep=2, scale=2.5)),
         _layer("latent_attention", _latent(4, 16, 24, 32, scale=0.4), _dense(80)),
         _layer("delta", _delta(4, 2, 24, 16, 3)),
-        _layer("latent_attention", _latent(2, 32, 8, 32, kv_from=1), _moe(24, 4, 3, scale=0.7)),
+        _layer("latent_attention", _latent(2, 32, 8, 32, scale=0.25, kv_from=1), _moe(24, 4, 3, scale=0.7)),
         _layer("mamba2", _mamba(2, 40, 16, 1, 4, 2), _dense(48)),
         _layer("latent_attention", _latent(3, 8, 16, 48)),
         _layer("latent_attention", _latent(5, 16, 8, 48, kv_from=5), _dense(32)),

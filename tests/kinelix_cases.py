@@ -86,6 +86,17 @@ RAW = {
         _layer("delta", _delta(6, 3, 20, 12, 5)),
         _layer("latent_attention", _latent(7, 12, 20, 36, kv_from=0)),
     ], eps=1e-4, scale=0.5, cap=30.0),
+    # sizes at the edges of what the kernels choose between: more heads than a decode tile
+    # holds and exactly as many, a latent rank the tensor-core kernels refuse beside one they
+    # take, matrices of 256 and of 192 rows, many experts in many groups, three experts in one
+    "wide": _model(192, 300, [
+        _layer("latent_attention", _latent(20, 16, 24, 64, scale=0.3), _moe(48, 64, 8, count=8, keep=4, scale=0.5)),
+        _layer("mamba2", _mamba(4, 48, 256, 4, 4, 2), _dense(200)),
+        _layer("delta", _delta(4, 2, 192, 48, 2)),
+        _layer("latent_attention", _latent(3, 40, 8, 96)),
+        _layer("latent_attention", _latent(20, 8, 8, 96, kv_from=3), _moe(40, 3, 2)),
+        _layer("latent_attention", _latent(16, 16, 16, 64, kv_from=0)),
+    ], scale=1.5, cap=25.0),
     # layer sizes of the order a real model has (few layers, a small vocabulary)
     "real": _model(512, 1000, [
         _layer("mamba2", _mamba(16, 64, 128, 2, 2, 4), _moe(256, 16, 4, count=4, keep=2, scale=2.0)),

@@ -13,7 +13,8 @@ import replay_cases
 from kernel_twins import TorchOps
 from kinelix_cases import RAW, kinelix_model, make_runner, replay_and_compare, requests_for
 
-LENGTHS = {"mix": (37, 70, 129, 45, 3, 66), "ones": (33, 64, 100, 41), "odd": (50, 7, 121, 33)}
+LENGTHS = {"mix": (37, 70, 129, 45, 3, 66), "ones": (33, 64, 100, 41), "odd": (50, 7, 121, 33),
+           "wide": (40, 90)}
 
 
 @pytest.mark.parametrize("name", ["only_mamba2", "only_delta", "only_latent", "only_moe"])
@@ -26,7 +27,7 @@ def test_each_layer_kind_alone(name):
                            steps, rows, 3e-5)
 
 
-@pytest.mark.parametrize("name", ["mix", "ones", "odd"])
+@pytest.mark.parametrize("name", ["mix", "ones", "odd", "wide"])
 @pytest.mark.parametrize("mode", ["whole", "decode_tail", "portions", "mixed"])
 def test_replay(name, mode):
     lengths = LENGTHS[name]

@@ -439,7 +439,8 @@ def test_expert_products(ops, twin, dtype, tokens, hidden, ff, experts, top):
 
 # ------------------------------------------------------------------------------ the model
 
-LENGTHS = {"mix": (37, 70, 129, 45, 3, 66), "ones": (33, 64, 150, 41, 90), "odd": (50, 7, 121, 33)}
+LENGTHS = {"mix": (37, 70, 129, 45, 3, 66), "ones": (33, 64, 150, 41, 90), "odd": (50, 7, 121, 33),
+           "wide": (40, 300, 17)}
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
@@ -454,14 +455,14 @@ def test_each_layer_kind_alone(ops, dtype, name):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("name", ["mix", "ones", "odd"])
+@pytest.mark.parametrize("name", ["mix", "ones", "odd", "wide"])
 @pytest.mark.parametrize("mode", ["whole", "decode_tail", "portions", "mixed"])
 def test_replay(ops, dtype, name, mode):
     lengths = LENGTHS[name]
     requests = requests_for(name, lengths)
     builder = getattr(replay_cases, mode)
     steps, rows = builder(requests, 512, seed=3) if mode == "mixed" else builder(requests)
-    page = {"mix": 16, "ones": 8, "odd": 4}[name]
+    page = {"mix": 16, "ones": 8, "odd": 4, "wide": 16}[name]
     replay_and_compare(make_runner(name, ops, "cuda", dtype, page=page), name, lengths, steps, rows,
                        tolerance_for(dtype, name, lengths))
 

@@ -432,13 +432,17 @@ expert_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_ld,
         const int stage = kt % TC_STAGES;
         const __nv_bfloat16* as = a_s + (stage * TC_BM + wr * 32) * TC_BK;
         const __nv_bfloat16* ws = w_s + stage * W_ROWS * TC_BK;
+        // a decode step's tiles hold a handful of rows: a warp whose 32 rows are all beyond
+        // the tile's has nothing to multiply (it still copies and meets the others)
+        if (wr * 32 >= rows) continue;
+        const bool second = wr * 32 + 16 < rows;
 #pragma unroll
         for (int kk = 0; kk < TC_BK / 16; ++kk) {
             uint32_t af[2][4];
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int r = i * 16 + (lane & 15), c = kk * 2 + (lane >> 4);
-                ldmatrix_x4(af[i], as + r * TC_BK + ((c ^ (r & 7)) * 8));
+                if (i == 0 || second) ldmatrix_x4(af[i], as + r * TC_BK + ((c ^ (r & 7)) * 8));
             }
 #pragma unroll
             for (int p = 0; p < PARTS; ++p) {
@@ -452,6 +456,7 @@ expert_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_ld,
                     ldmatrix_x4(bf, ws + r * TC_BK + ((c ^ (r & 7)) * 8));
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
+                        if (i == 1 && !second) continue;
                         mma_bf16_16816(acc[p][i][2 * j2], af[i], bf[0], bf[1]);
                         mma_bf16_16816(acc[p][i][2 * j2 + 1], af[i], bf[2], bf[3]);
                     }

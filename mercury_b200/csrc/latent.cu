@@ -83,20 +83,77 @@ head_linear_kernel(const TX* __restrict__ x, int ld, int offset, const TW* __res
             out[(int64_t)(t0 + tt) * heads * outs + h * outs + o] = from_float<TO>(acc[tt]);
 }
 
+// The same for the few tokens of a decode step, where the matrices have to be streamed once
+// and few blocks with long chains of loads would do it slowly: a block computes 32 outputs
+// of one head for up to 8 tokens, its four warps each taking a quarter of the inputs i; the
+// quarters are added in a fixed order through shared memory.
+template <typename TX, typename TW, typename TO>
+__global__ void __launch_bounds__(128)
+head_linear_few_kernel(const TX* __restrict__ x, int ld, int offset, const TW* __restrict__ w,
+                       TO* __restrict__ out, int tokens, int heads, int in, int outs) {
+    grid_dependency_sync();
+    extern __shared__ __align__(16) float fs[];            // x: [in][8], then partial sums
+    float* x_s = fs;
+    float* part = fs + in * 8;                              // [4][8][32]
+    const int per = (outs + 31) / 32;
+    const int otile = blockIdx.x % per;
+    const int h = blockIdx.x / per;
+    const int t0 = blockIdx.y * 8;
+    for (int idx = threadIdx.x; idx < 8 * in; idx += blockDim.x) {
+        const int tt = idx / in, i = idx - tt * in;
+        x_s[i * 8 + tt] =
+            t0 + tt < tokens ? to_float(x[(int64_t)(t0 + tt) * ld + offset + h * in + i]) : 0.f;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    const int o = otile * 32 + lane;
+    const int quarter = (in + 3) / 4;
+    const int i0 = slice * quarter, i1 = min(in, i0 + quarter);
+    float acc[8];
+#pragma unroll
+    for (int tt = 0; tt < 8; ++tt) acc[tt] = 0.f;
+    if (o < outs) {
+        const TW* wh = w + (int64_t)h * in * outs + o;
+#pragma unroll 8
+        for (int i = i0; i < i1; ++i) {
+            const float v = to_float(wh[(int64_t)i * outs]);
+            const float4 x0 = *reinterpret_cast<const float4*>(x_s + i * 8);
+            const float4 x1 = *reinterpret_cast<const float4*>(x_s + i * 8 + 4);
+            acc[0] = fmaf(v, x0.x, acc[0]); acc[1] = fmaf(v, x0.y, acc[1]);
+            acc[2] = fmaf(v, x0.z, acc[2]); acc[3] = fmaf(v, x0.w, acc[3]);
+            acc[4] = fmaf(v, x1.x, acc[4]); acc[5] = fmaf(v, x1.y, acc[5]);
+            acc[6] = fmaf(v, x1.z, acc[6]); acc[7] = fmaf(v, x1.w, acc[7]);
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < 8; ++tt) part[(slice * 8 + tt) * 32 + lane] = acc[tt];
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 8 * 32; idx += blockDim.x) {
+        const int l = idx & 31, tt = idx >> 5;
+        const int oo = otile * 32 + l;
+        if (oo >= outs || t0 + tt >= tokens) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int sl = 0; sl < 4; ++sl) v += part[(sl * 8 + tt) * 32 + l];
+        out[(int64_t)(t0 + tt) * heads * outs + h * outs + oo] = from_float<TO>(v);
+    }
+}
+
 template <typename TX, typename TW, typename TO>
 int launch_head_linear(const void* x, int ld, int offset, const void* w, void* out, int tokens,
                        int heads, int in, int outs, cudaStream_t s) {
-    const bool few = tokens <= 8;
-    const int tile = few ? 4 : 16;
-    const size_t smem = (size_t)tile * in * sizeof(float);
+    const bool few = tokens <= 16;
+    const int tile = few ? 8 : 16;
+    const size_t smem = (size_t)tile * in * sizeof(float) + (few ? 4 * 8 * 32 * sizeof(float) : 0);
     if (smem > 48 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
     const int rows = (tokens + tile - 1) / tile;
     if (rows > 65535) return MB_ERR_UNSUPPORTED_SIZE;
     dim3 grid(((outs + 127) / 128) * heads, rows);
-    if (few)
-        MB_LAUNCH((head_linear_kernel<TX, TW, TO, 4>), grid, 128, smem, s, (const TX*)x, ld, offset,
+    if (few) {
+        dim3 few_grid(((outs + 31) / 32) * heads, rows);
+        MB_LAUNCH((head_linear_few_kernel<TX, TW, TO>), few_grid, 128, smem, s, (const TX*)x, ld, offset,
                   (const TW*)w, (TO*)out, tokens, heads, in, outs);
-    else
+    } else
         MB_LAUNCH((head_linear_kernel<TX, TW, TO, 16>), grid, 128, smem, s, (const TX*)x, ld, offset,
                   (const TW*)w, (TO*)out, tokens, heads, in, outs);
     return launch_status();

@@ -557,9 +557,79 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float
     }
 }
 
+// The same with a block of 128 threads per (token, part), for parts of 256 features and more
+// (a warp alone would walk them in a long chain of dependent loads).
+template <typename TO>
+__global__ void __launch_bounds__(128)
+gated_group_norm_block_kernel(const float* __restrict__ y, const float* __restrict__ pre, int pre_ld,
+                              int gate_offset, const float* __restrict__ w, int wn, int groups,
+                              int size, float eps, int gate_first, TO* __restrict__ out) {
+    grid_dependency_sync();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x / groups, part = blockIdx.x - t * groups;
+    const int width = groups * size;
+    const float* yr = y + (int64_t)t * width + part * size;
+    const float* gr = pre + (int64_t)t * pre_ld + gate_offset + part * size;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < size; c += blockDim.x) {
+        float x = yr[c];
+        if (gate_first) x *= silu_f(gr[c]);
+        ss = fmaf(x, x, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.f / sqrtf(ss / (float)size + eps);
+    TO* orow = out + (int64_t)t * width + part * size;
+    for (int c = threadIdx.x; c < size; c += blockDim.x) {
+        const float gate = silu_f(gr[c]);
+        float x = yr[c];
+        if (gate_first) x *= gate;
+        x = x * rstd * w[(part * size + c) % wn];
+        if (!gate_first) x *= gate;
+        orow[c] = from_float<TO>(x);
+    }
+}
+
+// A step of few tokens per sequence (decoding): one thread per (sequence, channel) takes the
+// convolution of the step's tokens in turn and then brings the tail up to date, in one launch.
+__global__ void conv_act_update_kernel(const float* __restrict__ pre, int ld, int offset,
+                                       const float* __restrict__ w, const float* __restrict__ bias,
+                                       float* __restrict__ tail, int64_t tail_stride,
+                                       const int* __restrict__ q_start, const int* __restrict__ slots,
+                                       float* __restrict__ out, int channels, int taps, int act) {
+    grid_dependency_sync();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int seq = blockIdx.y;
+    const int begin = q_start[seq], n = q_start[seq + 1] - begin;
+    if (c >= channels || n <= 0) return;
+    float* mine = tail + (int64_t)slots[seq] * tail_stride + c;
+    // hist[j]: the input j tokens before the token in hand (hist[0] the token itself)
+    float hist[16], wk[16];
+    for (int j = 1; j < taps; ++j) hist[j] = mine[(int64_t)(j - 1) * channels];
+    for (int k = 0; k < taps; ++k) wk[k] = w[c * taps + k];
+    const float b = bias ? bias[c] : 0.f;
+    for (int t = 0; t < n; ++t) {
+        hist[0] = pre[(int64_t)(begin + t) * ld + offset + c];
+        float acc = 0.f;
+        for (int k = 0; k < taps; ++k) acc = fmaf(wk[k], hist[taps - 1 - k], acc);
+        if (bias) acc += b;
+        if (act == 1) acc = silu_f(acc);
+        out[(int64_t)(begin + t) * channels + c] = acc;
+        for (int j = taps - 1; j >= 1; --j) hist[j] = hist[j - 1];
+    }
+    for (int j = 1; j < taps; ++j) mine[(int64_t)(j - 1) * channels] = hist[j];
+}
+
 }  // namespace mb
 
 using namespace mb;
+
+// The convolution of every token of the step and the tail's update behind it: one launch for
+// steps of at most 8 tokens a sequence, two otherwise.
+MB_EXPORT int mb_conv_act_update(const float* pre, int ld, int offset, const float* w,
+                                 const float* bias, float* tail, long long tail_stride,
+                                 const int* q_start, const int* slots, const int* seq_of_token,
+                                 float* out, int tokens, int num_seqs, int max_q_len, int channels,
+                                 int taps, int act, void* stream);
 
 MB_EXPORT int mb_conv_act(const float* pre, int ld, int offset, const float* w, const float* bias,
                           const float* tail, long long tail_stride, const int* q_start,
@@ -581,6 +651,26 @@ MB_EXPORT int mb_conv_tail_update(const float* pre, int ld, int offset, float* t
     dim3 grid((channels + 127) / 128, num_seqs);
     MB_LAUNCH((conv_tail_update_kernel), grid, 128, 0, (cudaStream_t)stream, pre, ld, offset, tail,
               (int64_t)tail_stride, q_start, slots, channels, taps);
+    return launch_status();
+}
+
+MB_EXPORT int mb_conv_act_update(const float* pre, int ld, int offset, const float* w,
+                                 const float* bias, float* tail, long long tail_stride,
+                                 const int* q_start, const int* slots, const int* seq_of_token,
+                                 float* out, int tokens, int num_seqs, int max_q_len, int channels,
+                                 int taps, int act, void* stream) {
+    if (tokens <= 0 || channels <= 0 || num_seqs <= 0) return MB_OK;
+    if (taps < 1 || taps > 16 || num_seqs > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    if (max_q_len > 8) {
+        const int rc = mb_conv_act(pre, ld, offset, w, bias, tail, tail_stride, q_start, slots,
+                                   seq_of_token, out, tokens, channels, taps, act, stream);
+        if (rc != MB_OK) return rc;
+        return mb_conv_tail_update(pre, ld, offset, tail, tail_stride, q_start, slots, num_seqs,
+                                   channels, taps, stream);
+    }
+    dim3 grid((channels + 127) / 128, num_seqs);
+    MB_LAUNCH((conv_act_update_kernel), grid, 128, 0, (cudaStream_t)stream, pre, ld, offset, w, bias,
+              tail, (int64_t)tail_stride, q_start, slots, out, channels, taps, act);
     return launch_status();
 }
 
@@ -721,8 +811,19 @@ MB_EXPORT int mb_gated_group_norm(const float* y, const float* pre, int pre_ld, 
     if (groups <= 0 || size <= 0 || wn <= 0) return MB_ERR_UNSUPPORTED_SIZE;
     const long long warps = (long long)tokens * groups;
     const long long blocks = (warps + 7) / 8;
-    if (blocks > 0x7fffffffLL) return MB_ERR_UNSUPPORTED_SIZE;
+    if (warps > 0x7fffffffLL) return MB_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    if (size >= 256) {
+        if (out_dtype == MB_F32)
+            MB_LAUNCH((gated_group_norm_block_kernel<float>), (int)warps, 128, 0, s, y, pre, pre_ld,
+                      gate_offset, w, wn, groups, size, eps, gate_first, (float*)out);
+        else if (out_dtype == MB_BF16)
+            MB_LAUNCH((gated_group_norm_block_kernel<__nv_bfloat16>), (int)warps, 128, 0, s, y, pre,
+                      pre_ld, gate_offset, w, wn, groups, size, eps, gate_first, (__nv_bfloat16*)out);
+        else
+            return MB_ERR_BAD_DTYPE;
+        return launch_status();
+    }
     if (out_dtype == MB_F32)
         MB_LAUNCH((gated_group_norm_kernel<float>), (int)blocks, 256, 0, s, y, pre, pre_ld, gate_offset,
                   w, wn, groups, size, eps, gate_first, (float*)out, tokens);

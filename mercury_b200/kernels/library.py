@@ -117,6 +117,9 @@ _SIGNATURES = {
     "mb_softcap": [c_void_p, c_longlong, c_float, c_void_p],
     "mb_conv_act": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
                     c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_conv_act_update": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p],
     "mb_conv_tail_update": [c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
                             c_int, c_int, c_void_p],
     "mb_mamba2_scan": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,

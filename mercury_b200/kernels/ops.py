@@ -660,6 +660,20 @@ class CudaOps:
         self.launches += 1
 
     @_timed("recurrence")
+    def conv_act_update(self, pre, offset, conv, bias, tail, batch, out, act):
+        """`conv_act` and then `conv_tail_update`: one launch for steps of at most 8 tokens a
+        sequence (one thread per sequence and channel walks them), two otherwise."""
+        channels, taps = conv.shape
+        if act not in ("silu", None):
+            raise KernelError(f"conv_act: no activation {act!r}")
+        check(self.lib.mb_conv_act_update(
+            _ptr(pre), pre.shape[1], int(offset), _ptr(conv), _ptr(bias), _ptr(tail), tail.stride(0),
+            _ptr(batch.q_start), _ptr(batch.slots), _ptr(batch.seq_of_token), _ptr(out), out.shape[0],
+            batch.num_seqs, batch.max_q_len, channels, taps, 1 if act == "silu" else 0,
+            self._stream()), "conv_act_update")
+        self.launches += 1 if (batch.max_q_len <= 8 or taps <= 1) else 2
+
+    @_timed("recurrence")
     def conv_tail_update(self, pre, offset, channels, taps, tail, batch):
         """Bring the convolution's past inputs up to the end of the step."""
         if taps <= 1:

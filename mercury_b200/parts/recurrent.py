@@ -207,8 +207,7 @@ class Mamba2(Mixer):
         ops.linear(x, self.in_weight, None, pre)
         cells, tail = state[:, :self.cells], state[:, self.cells:]
         xbc = ctx.buffer("recurrent_conv", tokens, self.channels, dtype="float32")
-        ops.conv_act(pre, self.inner, self.conv, self.conv_bias, tail, ctx.batch, xbc, "silu")
-        ops.conv_tail_update(pre, self.inner, self.channels, self.taps, tail, ctx.batch)
+        ops.conv_act_update(pre, self.inner, self.conv, self.conv_bias, tail, ctx.batch, xbc, "silu")
         y = ctx.buffer("recurrent_y", tokens, self.inner, dtype="float32")
         ops.mamba2_scan(xbc, pre, self.proj - self.heads, self.dt_bias, self.neg_rate, self.skip,
                         (self.heads, self.head_dim, self.state_size, self.groups), cells,
@@ -277,8 +276,7 @@ class GatedDeltaRule(Mixer):
         ops.linear(x, self.in_weight, None, pre)
         cells, tail = state[:, :self.cells], state[:, self.cells:]
         qkv = ctx.buffer("recurrent_conv", tokens, self.channels, dtype="float32")
-        ops.conv_act(pre, 0, self.conv, None, tail, ctx.batch, qkv, "silu")
-        ops.conv_tail_update(pre, 0, self.channels, self.taps, tail, ctx.batch)
+        ops.conv_act_update(pre, 0, self.conv, None, tail, ctx.batch, qkv, "silu")
         o = ctx.buffer("recurrent_y", tokens, self.inner, dtype="float32")
         gate_at = self.channels
         ops.delta_rule_scan(qkv, pre, gate_at + self.inner, gate_at + self.inner + self.heads,

@@ -374,6 +374,10 @@ class TorchOps:
                 acc = acc * torch.sigmoid(acc)
             out[begin:end] = acc.to(out.dtype)
 
+    def conv_act_update(self, pre, offset, conv, bias, tail, batch, out, act):
+        self.conv_act(pre, offset, conv, bias, tail, batch, out, act)
+        self.conv_tail_update(pre, offset, conv.shape[0], conv.shape[1], tail, batch)
+
     def conv_tail_update(self, pre, offset, channels, taps, tail, batch):
         if taps <= 1:
             return

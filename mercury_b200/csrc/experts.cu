@@ -75,23 +75,18 @@ router_logits_kernel(const T* __restrict__ x, const float* __restrict__ router,
     }
 }
 
-// The choice, a warp per token. Shared memory per warp: s[E], choice[E], group score[E],
-// candidates[E].
-__global__ void route_select_kernel(const float* __restrict__ logits,
-                                    const float* __restrict__ correction, int* __restrict__ chosen,
-                                    float* __restrict__ weights, int tokens, int experts, int top,
-                                    int group_count, int group_keep, float route_scale) {
-    grid_dependency_sync();
-    extern __shared__ float sm[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= tokens) return;
-    float* s_s = sm + (size_t)warp * 4 * experts;
+// The choice of one token by one warp, from its logits. `work`: 4 * experts floats of shared
+// memory (s[E], choice[E], group score[E], candidates[E]).
+__device__ __forceinline__ void route_choose(const float* logits, const float* __restrict__ correction,
+                                             int* __restrict__ chosen, float* __restrict__ weights,
+                                             float* work, int lane, int64_t t, int experts, int top,
+                                             int group_count, int group_keep, float route_scale) {
+    float* s_s = work;
     float* choice_s = s_s + experts;
     float* group_s = choice_s + experts;
     float* cand_s = group_s + experts;
     for (int e = lane; e < experts; e += 32) {
-        const float s = 1.f / (1.f + expf(-logits[(int64_t)t * experts + e]));
+        const float s = 1.f / (1.f + expf(-logits[e]));
         s_s[e] = s;
         choice_s[e] = s + correction[e];
         cand_s[e] = -INFINITY;
@@ -137,6 +132,52 @@ __global__ void route_select_kernel(const float* __restrict__ logits,
         }
         __syncwarp();
     }
+}
+
+// A warp per token.
+__global__ void route_select_kernel(const float* __restrict__ logits,
+                                    const float* __restrict__ correction, int* __restrict__ chosen,
+                                    float* __restrict__ weights, int tokens, int experts, int top,
+                                    int group_count, int group_keep, float route_scale) {
+    grid_dependency_sync();
+    extern __shared__ float sm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= tokens) return;
+    route_choose(logits + (int64_t)t * experts, correction, chosen, weights,
+                 sm + (size_t)warp * 4 * experts, lane, t, experts, top, group_count, group_keep,
+                 route_scale);
+}
+
+// Few tokens (a decode step): logits and choice in one launch, a block of eight warps per
+// token. The warps take the experts in turn (a lane its share of the expert's row), the
+// logits meet in shared memory and the first warp chooses.
+template <typename T>
+__global__ void __launch_bounds__(256)
+route_token_kernel(const T* __restrict__ x, const float* __restrict__ router,
+                   const float* __restrict__ correction, int* __restrict__ chosen,
+                   float* __restrict__ weights, int hidden, int experts, int top, int group_count,
+                   int group_keep, float route_scale) {
+    grid_dependency_sync();
+    extern __shared__ float sm[];                  // x [hidden], logits [experts], work [4 experts]
+    float* x_s = sm;
+    float* logit_s = x_s + hidden;
+    const int t = blockIdx.x;
+    for (int k = threadIdx.x; k < hidden; k += blockDim.x) x_s[k] = to_float(x[(int64_t)t * hidden + k]);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int e = warp; e < experts; e += 8) {
+        const float* wr = router + (int64_t)e * hidden;
+        float acc = 0.f;
+#pragma unroll 4
+        for (int k = lane; k < hidden; k += 32) acc = fmaf(x_s[k], __ldg(wr + k), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) logit_s[e] = acc;
+    }
+    __syncthreads();
+    if (warp == 0)
+        route_choose(logit_s, correction, chosen, weights, logit_s + experts, lane, t, experts, top,
+                     group_count, group_keep, route_scale);
 }
 
 // One block sorts the step's pairs by expert. plan: [0] tiles in all, then tile_expert[cap],
@@ -572,6 +613,19 @@ MB_EXPORT int mb_route_experts(const void* x, int x_dtype, const float* router,
     const size_t smem = (size_t)warps * 4 * experts * sizeof(float);
     if (smem > 40 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    const size_t one = (size_t)(hidden + 5 * experts) * sizeof(float);
+    if (tokens <= 32 && one <= 48 * 1024) {
+        if (x_dtype == MB_F32)
+            MB_LAUNCH((route_token_kernel<float>), tokens, 256, one, s, (const float*)x, router, correction,
+                      chosen, weights, hidden, experts, top, group_count, group_keep, route_scale);
+        else if (x_dtype == MB_BF16)
+            MB_LAUNCH((route_token_kernel<__nv_bfloat16>), tokens, 256, one, s, (const __nv_bfloat16*)x,
+                      router, correction, chosen, weights, hidden, experts, top, group_count, group_keep,
+                      route_scale);
+        else
+            return MB_ERR_BAD_DTYPE;
+        return launch_status();
+    }
     // many tokens: four a block, so that an expert's row is read once for four of them
     const bool many = tokens > 64 && (size_t)4 * hidden * sizeof(float) <= 48 * 1024;
     const int rt = many ? 4 : 1;

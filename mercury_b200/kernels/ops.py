@@ -775,7 +775,8 @@ class CudaOps:
             _ptr(x), _flag(x.dtype), _ptr(router), _ptr(correction), _ptr(self._router_logits),
             _ptr(chosen), _ptr(weights), tokens, x.shape[1], experts, top, int(group_count),
             int(group_keep), float(route_scale), self._stream()), "route_experts")
-        self.launches += 2
+        fused = tokens <= 32 and (x.shape[1] + 5 * experts) * 4 <= 48 * 1024
+        self.launches += 1 if fused else 2
 
     @_timed("expert products")
     def expert_feed_forward(self, x, chosen, weights, gate_up, down, out, ctx):

@@ -67,6 +67,17 @@ __device__ __forceinline__ double slice_sum(double v) {
     return v;
 }
 
+// The same for a column shared by SL lanes (8, or the whole warp).
+template <int SL>
+__device__ __forceinline__ int row_in(int slice, int i) { return 4 * (slice + SL * (i >> 2)) + (i & 3); }
+
+template <int SL, typename S>
+__device__ __forceinline__ S lanes_sum(S v) {
+#pragma unroll
+    for (int o = 1; o < SL; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
 // ---- short causal convolution --------------------------------------------------------------
 // out[t][c] = act(sum_k w[c][k] * x[t - (taps - 1 - k)][c] + bias[c]), x = pre[:, offset + c]
 // (row stride ld). Inputs from before the step come from the tail: tail[slot][(j - 1) *
@@ -377,7 +388,10 @@ mamba2_apply_kernel(const float* __restrict__ xbc, const float* __restrict__ run
 // computed from the matrix as the token found it (A): S^T k = g A^T k and o = g A^T q +
 // u (k . q), so one pass over a column's rows gives both sums. S is [dim][vdim] at
 // cells[slot][(head * dim + d) * vdim + p].
-template <int DPT, typename S>
+// SL: the lanes that share a column, 8 as described above or 32 (one column a warp, four rows a
+// lane at 128 rows): a quarter of the instructions per token and warp and four times the
+// warps, for steps that bring too few (sequence, head) pairs to fill the machine otherwise.
+template <int DPT, typename S, int SL = SS_SLICES>
 __global__ void __launch_bounds__(512)
 delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ pre, int pre_ld,
                        int beta_offset, int decay_offset, const float* __restrict__ dt_bias,
@@ -388,8 +402,8 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
                        int chunks_per_head) {
     grid_dependency_sync();
     extern __shared__ __align__(16) float sm[];
-    constexpr int DP = DPT * SS_SLICES;
-    const int cols = (blockDim.x >> 5) * 4;
+    constexpr int DP = DPT * SL;
+    const int cols = (blockDim.x >> 5) * (32 / SL);
     // two stages of: q [SS_TILE][DP], k [SS_TILE][DP], v [SS_TILE][cols], raw beta and decay
     // inputs [2][SS_TILE]
     const int stage_floats = 2 * SS_TILE * DP + SS_TILE * cols + 2 * SS_TILE;
@@ -400,7 +414,7 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
     const int begin = q_start[seq], end = q_start[seq + 1];
     if (begin >= end) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
-    const int slice = lane & 7, p_local = warp * 4 + (lane >> 3);
+    const int slice = lane & (SL - 1), p_local = warp * (32 / SL) + lane / SL;
     const int p = chunk * cols + p_local;
     const bool live = p < vdim;
     const int qk = key_heads * dim, inner = heads * vdim, width = 2 * qk + inner;
@@ -409,7 +423,7 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
     S s[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = row_of(slice, i);
+        const int d = row_in<SL>(slice, i);
         s[i] = (live && d < dim) ? (S)mine[(int64_t)d * vdim + p] : (S)0;
     }
     const float rate = neg_rate[head], bias = dt_bias[head];
@@ -486,8 +500,8 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
             S pa[4] = {(S)0, (S)0, (S)0, (S)0}, pb[4] = {(S)0, (S)0, (S)0, (S)0};
 #pragma unroll
             for (int j = 0; j < DPT / 4; ++j) {
-                kv[j] = kt[SS_SLICES * j];
-                const float4 qv = qt[SS_SLICES * j];
+                kv[j] = kt[SL * j];
+                const float4 qv = qt[SL * j];
                 pa[0] = fma(s[4 * j], (S)kv[j].x, pa[0]);
                 pa[1] = fma(s[4 * j + 1], (S)kv[j].y, pa[1]);
                 pa[2] = fma(s[4 * j + 2], (S)kv[j].z, pa[2]);
@@ -497,8 +511,8 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
                 pb[2] = fma(s[4 * j + 2], (S)qv.z, pb[2]);
                 pb[3] = fma(s[4 * j + 3], (S)qv.w, pb[3]);
             }
-            const S a = slice_sum((pa[0] + pa[1]) + (pa[2] + pa[3]));
-            const S b = slice_sum((pb[0] + pb[1]) + (pb[2] + pb[3]));
+            const S a = lanes_sum<SL, S>((pa[0] + pa[1]) + (pa[2] + pa[3]));
+            const S b = lanes_sum<SL, S>((pb[0] + pb[1]) + (pb[2] + pb[3]));
             const S g = g_s[tt];
             const S u = (S)beta_s[tt] * ((S)v_s[tt * cols + p_local] - g * a);
 #pragma unroll
@@ -515,7 +529,7 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
     }
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = row_of(slice, i);
+        const int d = row_in<SL>(slice, i);
         if (live && d < dim) mine[(int64_t)d * vdim + p] = (float)s[i];
     }
 }
@@ -794,6 +808,26 @@ MB_EXPORT int mb_delta_rule_scan(const float* qkv, const float* pre, int pre_ld,
                       (int64_t)cell_stride, q_start, slots, out, heads, key_heads, dim, vdim,      \
                       chunks);                                                                     \
     } while (0)
+    // few (sequence, head) pairs and matrices of 128 rows or 256: a column per warp
+    if (!precise && dim > 64 && (long long)heads * ((vdim + 4 * warps - 1) / (4 * warps)) * num_seqs < 148) {
+        const int wide_warps = vdim < 8 ? vdim : 8;
+        const int wide_chunks = (vdim + wide_warps - 1) / wide_warps;
+        dim3 wide_grid(heads * wide_chunks, num_seqs);
+#define MB_DR_WIDE(DPT)                                                                            \
+    do {                                                                                           \
+        const size_t smem = (size_t)2 * (2 * SS_TILE * DPT * 32 + SS_TILE * wide_warps +           \
+                                         2 * SS_TILE) * sizeof(float);                             \
+        if (!allow_smem(delta_rule_scan_kernel<DPT, float, 32>, smem)) return MB_ERR_UNSUPPORTED_SIZE; \
+        MB_LAUNCH((delta_rule_scan_kernel<DPT, float, 32>), wide_grid, wide_warps * 32, smem, s, qkv, \
+                  pre, pre_ld, beta_offset, decay_offset, dt_bias, neg_rate, unit_eps, cells,      \
+                  (int64_t)cell_stride, q_start, slots, out, heads, key_heads, dim, vdim,          \
+                  wide_chunks);                                                                    \
+    } while (0)
+        if (dim <= 128) MB_DR_WIDE(4);
+        else MB_DR_WIDE(8);
+#undef MB_DR_WIDE
+        return launch_status();
+    }
     if (dim <= 32) MB_DR_CASE(4);
     else if (dim <= 64) MB_DR_CASE(8);
     else if (dim <= 128) MB_DR_CASE(16);

@@ -198,7 +198,8 @@ def test_mamba2_long_portions_in_runs(ops, twin, heads, vdim, n, groups):
 
 @pytest.mark.parametrize("precise", [False, True], ids=["float", "double"])
 @pytest.mark.parametrize("heads,key_heads,dim,vdim,taps", [(4, 2, 24, 16, 3), (3, 3, 16, 32, 1), (6, 3, 20, 12, 5),
-                                                           (2, 1, 130, 72, 2), (8, 4, 128, 128, 4)])
+                                                           (2, 1, 130, 72, 2), (8, 4, 128, 128, 4),
+                                                           (2, 2, 256, 20, 3), (1, 1, 100, 5, 2)])
 def test_convolution_and_delta_rule_over_steps(ops, twin, precise, heads, key_heads, dim, vdim, taps):
     qk, inner = key_heads * dim, heads * vdim
     channels = 2 * qk + inner

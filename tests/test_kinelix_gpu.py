@@ -356,15 +356,18 @@ def test_one_far_key_stands_out_and_a_sink_takes_its_share(ops, dtype, far, kv_l
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("tokens,heads,cols,outs", [(1, 4, 16, 32), (7, 3, 20, 36), (33, 8, 64, 128),
-                                                    (300, 2, 130, 9), (9, 16, 128, 200)])
+                                                    (300, 2, 130, 9), (9, 16, 128, 200),
+                                                    (300, 6, 64, 128), (515, 14, 128, 64)])
 def test_head_linear(ops, twin, dtype, tokens, heads, cols, outs):
-    x32 = rand((tokens, 5 + heads * cols), torch.float32, 110)
+    x32 = rand((tokens, 8 + heads * cols), torch.float32, 110)
     w = rand((heads, cols, outs), dtype, 111, 0.2)
-    for x, offset in ((x32, 5), (x32[:, 5:].to(dtype).contiguous(), 0)):
+    for x, offset in ((x32, 8), (x32[:, 8:].to(dtype).contiguous(), 0)):
         got = torch.empty((tokens, heads * outs), dtype=dtype, device="cuda")
         want = torch.empty_like(got)
         ops.head_linear(x, offset, w, got)
-        twin.head_linear(x, offset, w, want)
+        # from 256 tokens on the bfloat16 engine hands the rows to the library in bfloat16
+        seen = x.to(dtype).to(x.dtype) if (dtype == torch.bfloat16 and tokens >= 256) else x
+        twin.head_linear(seen, offset, w, want)
         close(got, want, dtype, "per-head product", 1e-5)
 
 

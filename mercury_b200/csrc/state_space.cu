@@ -408,7 +408,14 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
     // inputs [2][SS_TILE]
     const int stage_floats = 2 * SS_TILE * DP + SS_TILE * cols + 2 * SS_TILE;
     __shared__ float beta_s[SS_TILE], kq_s[SS_TILE];
+    __shared__ float kk_s[SS_TILE], kq_next_s[SS_TILE];   // k_t . k_(t+1) and k_t . q_(t+1), t even
     __shared__ S g_s[SS_TILE];
+    // Two tokens per round where a lane's rows are few: both tokens' sums are taken against
+    // the matrix as the first of them found it (A): with a_0 = A^T k_0 and a_1 = A^T k_1,
+    //   u_0 = beta_0 (v_0 - g_0 a_0),   u_1 = beta_1 (v_1 - g_1 (g_0 a_1 + u_0 (k_0 . k_1)))
+    // and the same for the read-outs, so that the sums over the lanes (the longest stretch of
+    // a token's chain) are taken for two tokens side by side.
+    constexpr bool PAIRS = DPT <= 8;
     const int head = blockIdx.x / chunks_per_head, chunk = blockIdx.x - head * chunks_per_head;
     const int seq = blockIdx.y;
     const int begin = q_start[seq], end = q_start[seq + 1];
@@ -493,7 +500,72 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
             if (lane == 0) kq_s[tt] = cross * rq * rk;
         }
         __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
+        int first_single = 0;
+        if (PAIRS) {
+            for (int tt = 2 * warp; tt + 1 < nt; tt += 2 * warps) {
+                float kk = 0.f, kq = 0.f;
+                for (int d = lane; d < dim; d += 32) {
+                    const float k0 = k_s[tt * DP + d];
+                    kk = fmaf(k0, k_s[(tt + 1) * DP + d], kk);
+                    kq = fmaf(k0, q_s[(tt + 1) * DP + d], kq);
+                }
+                kk = warp_sum(kk);
+                kq = warp_sum(kq);
+                if (lane == 0) {
+                    kk_s[tt] = kk;
+                    kq_next_s[tt] = kq;
+                }
+            }
+            __syncthreads();
+            for (int tt = 0; tt + 1 < nt; tt += 2) {
+                const float4* q0 = reinterpret_cast<const float4*>(q_s + tt * DP) + slice;
+                const float4* k0 = reinterpret_cast<const float4*>(k_s + tt * DP) + slice;
+                const float4* q1 = reinterpret_cast<const float4*>(q_s + (tt + 1) * DP) + slice;
+                const float4* k1 = reinterpret_cast<const float4*>(k_s + (tt + 1) * DP) + slice;
+                float4 k0v[DPT / 4], k1v[DPT / 4];
+                S a0 = (S)0, a1 = (S)0, b0 = (S)0, b1 = (S)0;
+#pragma unroll
+                for (int j = 0; j < DPT / 4; ++j) {
+                    k0v[j] = k0[SL * j];
+                    k1v[j] = k1[SL * j];
+                    const float4 q0v = q0[SL * j], q1v = q1[SL * j];
+                    a0 += (s[4 * j] * (S)k0v[j].x + s[4 * j + 1] * (S)k0v[j].y) +
+                          (s[4 * j + 2] * (S)k0v[j].z + s[4 * j + 3] * (S)k0v[j].w);
+                    a1 += (s[4 * j] * (S)k1v[j].x + s[4 * j + 1] * (S)k1v[j].y) +
+                          (s[4 * j + 2] * (S)k1v[j].z + s[4 * j + 3] * (S)k1v[j].w);
+                    b0 += (s[4 * j] * (S)q0v.x + s[4 * j + 1] * (S)q0v.y) +
+                          (s[4 * j + 2] * (S)q0v.z + s[4 * j + 3] * (S)q0v.w);
+                    b1 += (s[4 * j] * (S)q1v.x + s[4 * j + 1] * (S)q1v.y) +
+                          (s[4 * j + 2] * (S)q1v.z + s[4 * j + 3] * (S)q1v.w);
+                }
+#pragma unroll
+                for (int o = 1; o < SL; o <<= 1) {         // four sums side by side
+                    a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+                    a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+                    b0 += __shfl_xor_sync(0xffffffffu, b0, o);
+                    b1 += __shfl_xor_sync(0xffffffffu, b1, o);
+                }
+                const S g0 = g_s[tt], g1 = g_s[tt + 1];
+                const S u0 = (S)beta_s[tt] * ((S)v_s[tt * cols + p_local] - g0 * a0);
+                const S u1 = (S)beta_s[tt + 1] *
+                             ((S)v_s[(tt + 1) * cols + p_local] - g1 * (g0 * a1 + u0 * (S)kk_s[tt]));
+                const S both = g1 * g0, c0 = g1 * u0;
+#pragma unroll
+                for (int j = 0; j < DPT / 4; ++j) {
+                    s[4 * j] = fma(both, s[4 * j], fma((S)k0v[j].x, c0, (S)k1v[j].x * u1));
+                    s[4 * j + 1] = fma(both, s[4 * j + 1], fma((S)k0v[j].y, c0, (S)k1v[j].y * u1));
+                    s[4 * j + 2] = fma(both, s[4 * j + 2], fma((S)k0v[j].z, c0, (S)k1v[j].z * u1));
+                    s[4 * j + 3] = fma(both, s[4 * j + 3], fma((S)k0v[j].w, c0, (S)k1v[j].w * u1));
+                }
+                if (slice == 0 && live) {
+                    float* at = out + (int64_t)(t0 + tt) * inner + head * vdim + p;
+                    at[0] = (float)fma(u0, (S)kq_s[tt], g0 * b0);
+                    at[inner] = (float)fma(u1, (S)kq_s[tt + 1], g1 * (g0 * b1 + u0 * (S)kq_next_s[tt]));
+                }
+            }
+            first_single = nt & ~1;             // an odd tile leaves its last token
+        }
+        for (int tt = first_single; tt < nt; ++tt) {
             const float4* qt = reinterpret_cast<const float4*>(q_s + tt * DP) + slice;
             const float4* kt = reinterpret_cast<const float4*>(k_s + tt * DP) + slice;
             float4 kv[DPT / 4];

@@ -669,7 +669,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
 // batch walks at 2048-token contexts, and with all of them in shared memory before the kernel
 // in front is done nothing is copied inside the loop (16 copies of 16 bytes per thread and
 // tile there: some 2000 cycles a tile).
-template <int D, bool FED, bool TWO, int STG>
+template <int D, bool FED, bool TWO, int STG, bool SINKS>
 __global__ void __launch_bounds__(FED ? 160 : 128)
 attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                                 const __grid_constant__ CUtensorMap map_v,
@@ -1391,7 +1391,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
         }
         // a sink joins the denominator once: here when the block has all the keys, else where
         // the ranges are merged
-        if (sinks && num_splits == 1 && r < rows && big > -INFINITY)
+        if (SINKS && sinks && num_splits == 1 && r < rows && big > -INFINITY)
             sum += fast_exp2(sinks[kvh * group + hg] * 1.4426950408889634f - big);
         if (PUSH && num_splits > 1) {
             // row r is finished by block r / per_block: its landing slot for this range
@@ -1479,7 +1479,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                 denom += w * lz[z];
             }
             const int tok = r / group, hg = r - tok * group;
-            if (sinks && big > -INFINITY) denom += fast_exp2(sinks[kvh * group + hg] * 1.4426950408889634f - big);
+            if (SINKS && sinks && big > -INFINITY) denom += fast_exp2(sinks[kvh * group + hg] * 1.4426950408889634f - big);
             out[((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + c] =
                 __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
         }
@@ -1522,7 +1522,7 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k,
                 denom += w * lz[z];
             }
             const int tok = r / group, hg = r - tok * group;
-            if (sinks && big > -INFINITY) denom += fast_exp2(sinks[kvh * group + hg] * 1.4426950408889634f - big);
+            if (SINKS && sinks && big > -INFINITY) denom += fast_exp2(sinks[kvh * group + hg] * 1.4426950408889634f - big);
             out[((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D + c] =
                 __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
         }
@@ -1543,7 +1543,7 @@ static int device_sms() {
     return sms;
 }
 
-template <int D, bool FED, bool TWO, int STG>
+template <int D, bool FED, bool TWO, int STG, bool SINKS>
 int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const void* k_pages,
                                     const void* v_pages, const int* table, int max_pages,
                                     const int* q_start, const int* kv_len, void* out, int n_q, int n_kv,
@@ -1572,7 +1572,7 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
                         (D == 64 ? (size_t)(16 * D + 16 * 2) * sizeof(float) : 0) + (FED ? 1024 : 0);
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
-        if (cudaFuncSetAttribute(attention_decode_cluster_kernel<D, FED, TWO, STG>,
+        if (cudaFuncSetAttribute(attention_decode_cluster_kernel<D, FED, TWO, STG, SINKS>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return MB_ERR_UNSUPPORTED_SIZE;
         raised = true;
@@ -1591,7 +1591,7 @@ int launch_attention_decode_cluster(const void* qkv, int q_row_stride, const voi
     }
     config.attrs = attrs;
     config.numAttrs = num_attrs;
-    cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D, FED, TWO, STG>, map_k, map_v, (const bf*)qkv,
+    cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D, FED, TWO, STG, SINKS>, map_k, map_v, (const bf*)qkv,
                        q_row_stride, (const bf*)k_pages, (const bf*)v_pages, table, max_pages, q_start,
                        kv_len, (bf*)out, n_q, n_kv, page_size, scale, window, cos_t, sin_t, raw, store,
                        error, sinks);
@@ -1699,11 +1699,13 @@ MB_EXPORT int mb_paged_attention_decode_cluster_sinks(
                      page_size <= MMA_BN && (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
     // (the longest portion bounds every sequence's rows: one column tile of 8 rows, or two)
     const bool two = max_q_len * (n_q / n_kv) > 8;
+    // (with sinks another instantiation: the one without stays as it was compiled before)
+#define MB_DC_ARGS(FED_) qkv, q_row_stride, k_pages, v_pages, table, max_pages, q_start, kv_len, out, n_q, \
+                         n_kv, page_size, scale, window, num_seqs, cluster, cos_t, sin_t, raw, store, \
+                         FED_ ? num_pages : 0, FED_ ? error : nullptr, sinks, s
 #define MB_DC_LAUNCH(D_, FED_, TWO_, STG_)                                                            \
-    launch_attention_decode_cluster<D_, FED_, TWO_, STG_>(qkv, q_row_stride, k_pages, v_pages, table, max_pages, \
-                                                    q_start, kv_len, out, n_q, n_kv, page_size, scale, \
-                                                    window, num_seqs, cluster, cos_t, sin_t, raw, store, \
-                                                    FED_ ? num_pages : 0, FED_ ? error : nullptr, sinks, s)
+    (sinks ? launch_attention_decode_cluster<D_, FED_, TWO_, STG_, true>(MB_DC_ARGS(FED_))            \
+           : launch_attention_decode_cluster<D_, FED_, TWO_, STG_, false>(MB_DC_ARGS(FED_)))
     // (TMA-fed: eight half stages at head size 64, four at 128, where eight would leave an SM
     // to one block: measured at 1.5B sizes with no more blocks than SMs, 8 sequences, 1.32 ms per
     // step with four and 1.44 with eight)
@@ -1719,6 +1721,7 @@ MB_EXPORT int mb_paged_attention_decode_cluster_sinks(
         return two ? MB_DC_LAUNCH(128, false, true, 5) : MB_DC_LAUNCH(128, false, false, 5);
     return two ? MB_DC_LAUNCH(128, false, true, 3) : MB_DC_LAUNCH(128, false, false, 3);
 #undef MB_DC_LAUNCH
+#undef MB_DC_ARGS
 }
 
 MB_EXPORT int mb_paged_attention_decode_cluster(const void* qkv, int q_row_stride, const void* k_pages,
